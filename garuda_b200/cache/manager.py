@@ -16,7 +16,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from ..csrc.build import load_host_module
-from ..parts.base import LayerCache, PagedKV, FixedState
+from ..parts.base import LayerCache, PagedKV, PagedLatent, FixedState
 
 
 @dataclass
@@ -53,10 +53,17 @@ class PagedCache:
         self.v_pools: List[torch.Tensor] = []
         self.call_group: Dict[int, tuple] = {}
         for gi, g in enumerate(self.groups):
-            shape = (len(g.calls), pages, g.need.kv_heads, ps, g.need.head_dim)
-            if allocate:
-                self.k_pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
-                self.v_pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
+            if isinstance(g.need, PagedLatent):
+                # one vector per position, shared by the heads: a single pool (there is no value pool)
+                shape = (len(g.calls), pages, 1, ps, g.need.width)
+                if allocate:
+                    self.k_pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
+                    self.v_pools.append(None)
+            else:
+                shape = (len(g.calls), pages, g.need.kv_heads, ps, g.need.head_dim)
+                if allocate:
+                    self.k_pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
+                    self.v_pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
             for j, call in enumerate(g.calls):
                 self.call_group[call] = (gi, j)
         self.states: Dict[int, torch.Tensor] = {}
@@ -87,7 +94,8 @@ class PagedCache:
 
     def bytes_per_position(self) -> int:
         item = self.dtype.itemsize
-        return sum(2 * len(g.calls) * g.need.kv_heads * g.need.head_dim * item for g in self.groups)
+        return sum(len(g.calls) * (g.need.width if isinstance(g.need, PagedLatent)
+                                   else 2 * g.need.kv_heads * g.need.head_dim) * item for g in self.groups)
 
     # ---- views for a step ------------------------------------------------------
     def layer_caches(self, block_tables: Sequence[torch.Tensor]) -> List[Optional[LayerCache]]:
@@ -100,9 +108,10 @@ class PagedCache:
             src = i if call.reads_cache_of is None else call.reads_cache_of
             if need is None:
                 out.append(None)
-            elif isinstance(need, PagedKV):
+            elif isinstance(need, (PagedKV, PagedLatent)):
                 gi, j = self.call_group[src]
-                out.append(LayerCache(need=need, k=self.k_pools[gi][j], v=self.v_pools[gi][j],
+                v_pool = self.v_pools[gi]
+                out.append(LayerCache(need=need, k=self.k_pools[gi][j], v=None if v_pool is None else v_pool[j],
                                       block_table=block_tables[gi], page_size=self.page_size,
                                       writes=call.reads_cache_of is None))
             else:

@@ -42,9 +42,13 @@ def registered_architectures():
 
 def architecture_of(config_dict: dict) -> str:
     archs = config_dict.get("architectures")
-    if not archs:
-        raise ConfigError("config.json is missing 'architectures'")
-    return archs[0]
+    if archs:
+        return archs[0]
+    # some designs name themselves with a single string
+    name = config_dict.get("architecture")
+    if isinstance(name, str) and name:
+        return name
+    raise ConfigError("config.json is missing 'architectures'")
 
 
 def read_model_config(config_dict: dict):

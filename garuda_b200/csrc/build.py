@@ -34,6 +34,8 @@ CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall"]
 KERNEL_LIBS: Dict[str, List[str]] = {
     "garuda_core": ["elementwise.cu", "gemm_simple.cu", "attention_simple.cu", "sampling.cu"],
     "garuda_tc": ["gemm_tcgen05.cu"],
+    # attention over a cached latent and routed experts: built when a model first uses them
+    "garuda_mixers": ["latent.cu", "moe.cu"],
 }
 HOST_SOURCES = ["cache_manager.cpp", "scheduler.cpp", "step_batch.cpp", "bindings.cpp"]
 

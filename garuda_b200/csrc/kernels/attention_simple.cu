@@ -14,15 +14,17 @@
 namespace {
 
 constexpr int WARPS = 4;
-constexpr int MAX_HD = 256;
 
-template <typename T>
+// MAX_HD: the widest head this instance takes. A value row is `v_hd` wide in its pool, of which the
+// first `vd` channels are summed (vd = v_hd = hd for ordinary attention; a mixer whose keys and
+// values are parts of one cached vector passes the same pool twice and a narrower vd).
+template <typename T, int MAX_HD>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_simple_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                         const int32_t* __restrict__ block_table, int table_width,
                         const int32_t* __restrict__ cu_q, const int32_t* __restrict__ kv_lens,
                         const int32_t* __restrict__ token_req, T* __restrict__ out, int Hq, int Hkv, int hd,
-                        float scale, int window, int page_size) {
+                        int v_hd, int vd, float scale, int window, int page_size) {
   __shared__ float q_s[WARPS][MAX_HD];
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -39,7 +41,7 @@ attention_simple_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, c
   for (int c = lane; c < hd; c += 32) q_s[warp][c] = gb::to_float<T>(qr[c]);
   __syncwarp();
 
-  const int nacc = (hd + 31) / 32;
+  const int nacc = (vd + 31) / 32;
   float acc[MAX_HD / 32];
 #pragma unroll
   for (int i = 0; i < MAX_HD / 32; ++i) acc[i] = 0.f;
@@ -72,39 +74,49 @@ attention_simple_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, c
       const float pj = __shfl_sync(0xffffffffu, p, jj);
       const long long rj = __shfl_sync(0xffffffffu, row, jj);
       if (rj < 0) continue;
-      const T* vr = v_pool + rj * hd;
+      const T* vr = v_pool + rj * v_hd;
 #pragma unroll
       for (int i = 0; i < MAX_HD / 32; ++i) {
         const int c = lane + 32 * i;
-        if (i < nacc && c < hd) acc[i] = fmaf(pj, gb::to_float<T>(vr[c]), acc[i]);
+        if (i < nacc && c < vd) acc[i] = fmaf(pj, gb::to_float<T>(vr[c]), acc[i]);
       }
     }
   }
   const float inv = l > 0.f ? 1.0f / l : 0.f;
-  T* o = out + ((size_t)t * Hq + h) * hd;
+  T* o = out + ((size_t)t * Hq + h) * vd;
 #pragma unroll
   for (int i = 0; i < MAX_HD / 32; ++i) {
     const int c = lane + 32 * i;
-    if (i < nacc && c < hd) o[c] = gb::from_float<T>(acc[i] * inv);
+    if (i < nacc && c < vd) o[c] = gb::from_float<T>(acc[i] * inv);
   }
 }
 
 }  // namespace
 
+// v_hd: width of a value row in its pool; vd: how many of its first channels are the value
+// (out is [T, Hq, vd]). Ordinary attention passes hd for both.
 GB_EXPORT int gb_attention_simple(const void* q, const void* k_pool, const void* v_pool, int dtype,
                                   const int32_t* block_table, int table_width, const int32_t* cu_q,
                                   const int32_t* kv_lens, const int32_t* token_req, void* out, int T,
-                                  int Hq, int Hkv, int hd, float scale, int window, int page_size,
-                                  cudaStream_t stream) {
+                                  int Hq, int Hkv, int hd, int v_hd, int vd, float scale, int window,
+                                  int page_size, cudaStream_t stream) {
   if (T <= 0) return GB_OK;
-  if (hd > MAX_HD || hd < 1)
-    return gb::fail(GB_UNSUPPORTED, "attention: head_dim %d is outside 1..%d", hd, MAX_HD);
+  constexpr int WIDEST = 1024;
+  if (hd > WIDEST || hd < 1)
+    return gb::fail(GB_UNSUPPORTED, "attention: head_dim %d is outside 1..%d", hd, WIDEST);
+  if (vd < 1 || vd > v_hd || vd > WIDEST)
+    return gb::fail(GB_BAD_ARGUMENT, "attention: %d value channels of rows %d wide", vd, v_hd);
   if (Hkv < 1 || Hq % Hkv) return gb::fail(GB_BAD_ARGUMENT, "attention: %d query heads for %d kv heads", Hq, Hkv);
   dim3 grid(T, (Hq + WARPS - 1) / WARPS);
   return GB_DISPATCH_DTYPE(dtype, TT, [&]() -> int {
-    attention_simple_kernel<TT><<<grid, WARPS * 32, 0, stream>>>(
-        (const TT*)q, (const TT*)k_pool, (const TT*)v_pool, block_table, table_width, cu_q, kv_lens,
-        token_req, (TT*)out, Hq, Hkv, hd, scale, window, page_size);
+    if (hd <= 256 && vd <= 256)
+      attention_simple_kernel<TT, 256><<<grid, WARPS * 32, 0, stream>>>(
+          (const TT*)q, (const TT*)k_pool, (const TT*)v_pool, block_table, table_width, cu_q, kv_lens,
+          token_req, (TT*)out, Hq, Hkv, hd, v_hd, vd, scale, window, page_size);
+    else
+      attention_simple_kernel<TT, WIDEST><<<grid, WARPS * 32, 0, stream>>>(
+          (const TT*)q, (const TT*)k_pool, (const TT*)v_pool, block_table, table_width, cu_q, kv_lens,
+          token_req, (TT*)out, Hq, Hkv, hd, v_hd, vd, scale, window, page_size);
     return gb::check_launch("attention_simple");
   });
 }

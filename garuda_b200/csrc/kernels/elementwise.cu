@@ -13,7 +13,7 @@ namespace {
 // ---------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int32_t* __restrict__ ids,
-                                 float* __restrict__ out, int d, int vocab) {
+                                 float* __restrict__ out, int d, int vocab, float scale) {
   gb::pdl_launch_dependents();
   gb::pdl_wait();
   const int t = blockIdx.x;
@@ -24,7 +24,7 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int32_t* __r
     return;
   }
   const T* row = table + (size_t)id * d;
-  for (int c = threadIdx.x; c < d; c += blockDim.x) o[c] = gb::to_float<T>(row[c]);
+  for (int c = threadIdx.x; c < d; c += blockDim.x) o[c] = gb::to_float<T>(row[c]) * scale;
 }
 
 // ------------------------------------------------------------------ rmsnorm
@@ -209,9 +209,27 @@ __global__ void rope_inplace_kernel(float* __restrict__ x, int row_stride, int h
 // ------------------------------------------------------------ SiLU-gate
 // gate_up rows hold either [gate(F) | up(F)] (group 0), or gate and up packed in groups of 64:
 // columns [128 q, 128 q + 64) gate features 64 q .., the next 64 their up values (group 64).
+// kind: GB_ACT_SILU  silu(g) * u;  GB_ACT_GELU_TANH  gelu_tanh(g) * u;
+// GB_ACT_CLAMPED_SWISH  g' = min(g, limit), u' = clamp(u, -limit, limit): g' * sigmoid(1.702 g') * (u' + 1).
+enum GbGateAct : int { GB_ACT_SILU = 0, GB_ACT_GELU_TANH = 1, GB_ACT_CLAMPED_SWISH = 2 };
+
+__device__ __forceinline__ float gelu_tanh(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+__device__ __forceinline__ float gate_act(int kind, float limit, float g, float u) {
+  if (kind == GB_ACT_GELU_TANH) return gelu_tanh(g) * u;
+  if (kind == GB_ACT_CLAMPED_SWISH) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return (g / (1.0f + expf(-1.702f * g))) * (u + 1.0f);
+  }
+  return (g / (1.0f + expf(-g))) * u;
+}
+
 template <typename IT, typename OT>
 __global__ void silu_mul_kernel(const IT* __restrict__ gate_up, OT* __restrict__ out, int M, int F, int group,
-                                int row_stride) {
+                                int row_stride, int kind, float limit) {
   const size_t n = (size_t)M * F;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const size_t m = i / F, f = i % F;
@@ -219,7 +237,7 @@ __global__ void silu_mul_kernel(const IT* __restrict__ gate_up, OT* __restrict__
     const size_t ui = group ? gi + group : F + f;
     const float g = gb::to_float<IT>(gate_up[m * row_stride + gi]);
     const float u = gb::to_float<IT>(gate_up[m * row_stride + ui]);
-    out[i] = gb::from_float<OT>((g / (1.0f + expf(-g))) * u);
+    out[i] = gb::from_float<OT>(gate_act(kind, limit, g, u));
   }
 }
 
@@ -229,6 +247,95 @@ __global__ void residual_add_kernel(float* __restrict__ x, const YT* __restrict_
     x[i] += gb::to_float<YT>(y[i]);
 }
 
+int grid_for(size_t n, int block);
+
+// ---------------------------------------------------------------- layer norm
+// Sum of a value over the block in a fixed order (warps, then the warps' sums): a row's result
+// does not depend on which other rows are in the batch.
+__device__ __forceinline__ float block_sum(float v, float* part) {
+  v = gb::warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();                       // `part` may still be read from the call before
+  if (lane == 0) part[warp] = v;
+  __syncthreads();
+  float t = lane < (blockDim.x >> 5) ? part[lane] : 0.f;
+  return gb::warp_sum(t);
+}
+
+// out = (x - mean) / sqrt(var + eps) * w + b, var the mean of the squared deviations (taken in a
+// second pass over the row, not as mean(x^2) - mean^2). One block per row, 32-bit throughout.
+template <typename WT, typename OT>
+__global__ void __launch_bounds__(256)
+layernorm_kernel(const float* __restrict__ x, const WT* __restrict__ w, const WT* __restrict__ b, float eps,
+                 OT* __restrict__ out, const int32_t* __restrict__ rows, int d) {
+  gb::pdl_launch_dependents();
+  gb::pdl_wait();
+  __shared__ float part[32];
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * d;
+  float s = 0.f;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) s += xr[c];
+  const float mean = block_sum(s, part) / (float)d;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    const float dv = xr[c] - mean;
+    ss = fmaf(dv, dv, ss);
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, part) / (float)d + eps);
+  OT* o = out + (size_t)r * d;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    const float bias = b ? gb::to_float<WT>(b[c]) : 0.f;
+    o[c] = gb::from_float<OT>(((xr[c] - mean) * inv) * gb::to_float<WT>(w[c]) + bias);
+  }
+}
+
+// x[t][c] += alpha * y[t][c] + row[c]; y or row may be absent
+template <typename YT, typename RT>
+__global__ void residual_axpy_kernel(float* __restrict__ x, const YT* __restrict__ y, float alpha,
+                                     const RT* __restrict__ row, size_t n, int d) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float v = x[i];
+    if (y) v = fmaf(alpha, gb::to_float<YT>(y[i]), v);
+    if (row) v += gb::to_float<RT>(row[i % d]);
+    x[i] = v;
+  }
+}
+
+// x[t] += alpha * y[t] / sqrt(mean(y[t]^2) + eps) * w: an RMS-normed branch added to the residual
+template <typename WT>
+__global__ void __launch_bounds__(256)
+rms_add_kernel(float* __restrict__ x, const float* __restrict__ y, const WT* __restrict__ w, float eps,
+               float alpha, int d) {
+  __shared__ float part[32];
+  const float* yr = y + (size_t)blockIdx.x * d;
+  float* xr = x + (size_t)blockIdx.x * d;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) ss = fmaf(yr[c], yr[c], ss);
+  const float inv = 1.0f / sqrtf(block_sum(ss, part) / (float)d + eps);
+  for (int c = threadIdx.x; c < d; c += blockDim.x)
+    xr[c] = fmaf(alpha, (yr[c] * inv) * gb::to_float<WT>(w[c]), xr[c]);
+}
+
+// out[t][j] = gelu_tanh(z[t][j]) * table[ids[t]][col0 + j]: a gate on a per-token table row
+template <typename IT, typename TT, typename OT>
+__global__ void gelu_gather_mul_kernel(const IT* __restrict__ z, const TT* __restrict__ table, int table_ld,
+                                       int col0, const int32_t* __restrict__ ids, OT* __restrict__ out, int T,
+                                       int dim, int vocab) {
+  const size_t n = (size_t)T * dim;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const int t = (int)(i / dim), j = (int)(i % dim);
+    const int id = ids[t];
+    const float e = (id >= 0 && id < vocab) ? gb::to_float<TT>(table[(size_t)id * table_ld + col0 + j]) : 0.f;
+    out[i] = gb::from_float<OT>(gelu_tanh(gb::to_float<IT>(z[i])) * e);
+  }
+}
+
+template <typename OT>
+__global__ void cast_kernel(const float* __restrict__ x, OT* __restrict__ out, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = gb::from_float<OT>(x[i]);
+}
+
 int grid_for(size_t n, int block) {
   size_t g = (n + block - 1) / block;
   return (int)(g > 148 * 16 ? 148 * 16 : (g ? g : 1));
@@ -236,12 +343,13 @@ int grid_for(size_t n, int block) {
 
 }  // namespace
 
+// out[t] = table[ids[t]] * scale (a model without an embedding multiplier passes 1)
 GB_EXPORT int gb_embedding(const void* table, int table_dtype, const int32_t* ids, float* out, int T,
-                           int d, int vocab, cudaStream_t stream) {
+                           int d, int vocab, float scale, cudaStream_t stream) {
   if (T <= 0) return GB_OK;
   return GB_DISPATCH_DTYPE(table_dtype, TT, [&]() -> int {
     return gb::check_pdl_launch(gb::launch_pdl(embedding_kernel<TT>, dim3(T), dim3(256), 0, stream, dim3(1, 1, 1),
-                                               (const TT*)table, ids, out, d, vocab), "embedding");
+                                               (const TT*)table, ids, out, d, vocab, scale), "embedding");
   });
 }
 
@@ -317,13 +425,26 @@ GB_EXPORT int gb_rope_inplace(float* x, int row_stride, int head_stride, int T, 
   return gb::check_launch("rope_inplace");
 }
 
+GB_EXPORT int gb_gated_act(const void* gate_up, int in_dtype, void* out, int out_dtype, int M, int F, int group,
+                           int row_stride, int kind, float limit, cudaStream_t stream) {
+  if (M <= 0 || F <= 0) return GB_OK;
+  if (kind < GB_ACT_SILU || kind > GB_ACT_CLAMPED_SWISH) return gb::fail(GB_BAD_ARGUMENT, "gated_act: kind %d", kind);
+  return GB_DISPATCH_DTYPE(in_dtype, IT, [&]() -> int {
+    return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
+      silu_mul_kernel<IT, OT><<<grid_for((size_t)M * F, 256), 256, 0, stream>>>(
+          (const IT*)gate_up, (OT*)out, M, F, group, row_stride, kind, limit);
+      return gb::check_launch("gated_act");
+    });
+  });
+}
+
 GB_EXPORT int gb_silu_mul(const void* gate_up, int in_dtype, void* out, int out_dtype, int M, int F, int group,
                           int row_stride, cudaStream_t stream) {
   if (M <= 0 || F <= 0) return GB_OK;
   return GB_DISPATCH_DTYPE(in_dtype, IT, [&]() -> int {
     return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
       silu_mul_kernel<IT, OT><<<grid_for((size_t)M * F, 256), 256, 0, stream>>>(
-          (const IT*)gate_up, (OT*)out, M, F, group, row_stride);
+          (const IT*)gate_up, (OT*)out, M, F, group, row_stride, GB_ACT_SILU, 0.f);
       return gb::check_launch("silu_mul");
     });
   });
@@ -334,5 +455,62 @@ GB_EXPORT int gb_residual_add(float* x, const void* y, int y_dtype, long long n,
   return GB_DISPATCH_DTYPE(y_dtype, YT, [&]() -> int {
     residual_add_kernel<YT><<<grid_for((size_t)n, 256), 256, 0, stream>>>(x, (const YT*)y, (size_t)n);
     return gb::check_launch("residual_add");
+  });
+}
+
+GB_EXPORT int gb_layernorm(const float* x, const void* w, const void* b, int w_dtype, float eps, void* out,
+                           int out_dtype, const int32_t* rows, int n_rows, int d, cudaStream_t stream) {
+  if (n_rows <= 0) return GB_OK;
+  return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
+    return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
+      return gb::check_pdl_launch(gb::launch_pdl(layernorm_kernel<WT, OT>, dim3(n_rows), dim3(d >= 1024 ? 256 : 128), 0,
+                                                 stream, dim3(1, 1, 1), x, (const WT*)w, (const WT*)b, eps, (OT*)out,
+                                                 rows, d), "layernorm");
+    });
+  });
+}
+
+GB_EXPORT int gb_residual_axpy(float* x, const void* y, int y_dtype, float alpha, const void* row, int row_dtype,
+                               int T, int d, cudaStream_t stream) {
+  if (T <= 0 || d <= 0) return GB_OK;
+  const size_t n = (size_t)T * d;
+  return GB_DISPATCH_DTYPE(y_dtype, YT, [&]() -> int {
+    return GB_DISPATCH_DTYPE(row_dtype, RT, [&]() -> int {
+      residual_axpy_kernel<YT, RT><<<grid_for(n, 256), 256, 0, stream>>>(x, (const YT*)y, alpha, (const RT*)row, n, d);
+      return gb::check_launch("residual_axpy");
+    });
+  });
+}
+
+GB_EXPORT int gb_rms_add(float* x, const float* y, const void* w, int w_dtype, float eps, float alpha, int T, int d,
+                         cudaStream_t stream) {
+  if (T <= 0) return GB_OK;
+  return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
+    rms_add_kernel<WT><<<T, d >= 1024 ? 256 : 128, 0, stream>>>(x, y, (const WT*)w, eps, alpha, d);
+    return gb::check_launch("rms_add");
+  });
+}
+
+GB_EXPORT int gb_gelu_gather_mul(const void* z, int z_dtype, const void* table, int table_dtype, int table_ld,
+                                 int col0, const int32_t* ids, void* out, int out_dtype, int T, int dim, int vocab,
+                                 cudaStream_t stream) {
+  if (T <= 0 || dim <= 0) return GB_OK;
+  if (col0 < 0 || col0 + dim > table_ld) return gb::fail(GB_BAD_ARGUMENT, "gelu_gather_mul: columns %d..%d of %d", col0, col0 + dim, table_ld);
+  return GB_DISPATCH_DTYPE(z_dtype, IT, [&]() -> int {
+    return GB_DISPATCH_DTYPE(table_dtype, TT, [&]() -> int {
+      return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
+        gelu_gather_mul_kernel<IT, TT, OT><<<grid_for((size_t)T * dim, 256), 256, 0, stream>>>(
+            (const IT*)z, (const TT*)table, table_ld, col0, ids, (OT*)out, T, dim, vocab);
+        return gb::check_launch("gelu_gather_mul");
+      });
+    });
+  });
+}
+
+GB_EXPORT int gb_cast(const float* x, void* out, int out_dtype, long long n, cudaStream_t stream) {
+  if (n <= 0) return GB_OK;
+  return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
+    cast_kernel<OT><<<grid_for((size_t)n, 256), 256, 0, stream>>>(x, (OT*)out, (size_t)n);
+    return gb::check_launch("cast");
   });
 }

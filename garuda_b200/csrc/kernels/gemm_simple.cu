@@ -14,7 +14,7 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;  // 256 threads, 4x4 ou
 template <typename IT, typename OT, bool ACCUMULATE>
 __global__ void __launch_bounds__(256)
 gemm_simple_kernel(const IT* __restrict__ a, const IT* __restrict__ w, OT* __restrict__ out, int M, int N,
-                   int K) {
+                   int K, float alpha) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -60,7 +60,7 @@ gemm_simple_kernel(const IT* __restrict__ a, const IT* __restrict__ w, OT* __res
       const int gn = n0 + tn + j;
       if (gn >= N) continue;
       OT* o = out + (size_t)gm * N + gn;
-      if (ACCUMULATE) *o = gb::from_float<OT>(gb::to_float<OT>(*o) + acc[i][j]);
+      if (ACCUMULATE) *o = gb::from_float<OT>(fmaf(alpha, acc[i][j], gb::to_float<OT>(*o)));
       else *o = gb::from_float<OT>(acc[i][j]);
     }
   }
@@ -68,10 +68,10 @@ gemm_simple_kernel(const IT* __restrict__ a, const IT* __restrict__ w, OT* __res
 
 }  // namespace
 
-// in_dtype: dtype of a and w; out_dtype: dtype of out. accumulate: out += product
-// (out must then be 32-bit: it is the residual stream).
+// in_dtype: dtype of a and w; out_dtype: dtype of out. accumulate: out += alpha * product
+// (out must then be 32-bit: it is the residual stream; alpha is a model's residual multiplier).
 GB_EXPORT int gb_gemm_simple(const void* a, const void* w, void* out, int M, int N, int K, int in_dtype,
-                             int out_dtype, int accumulate, cudaStream_t stream) {
+                             int out_dtype, int accumulate, float alpha, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return GB_OK;
   if (K <= 0) return gb::fail(GB_BAD_ARGUMENT, "gemm: K = %d", K);
   if (accumulate && out_dtype != GB_F32)
@@ -80,9 +80,9 @@ GB_EXPORT int gb_gemm_simple(const void* a, const void* w, void* out, int M, int
   return GB_DISPATCH_DTYPE(in_dtype, IT, [&]() -> int {
     return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
       if (accumulate)
-        gemm_simple_kernel<IT, OT, true><<<grid, 256, 0, stream>>>((const IT*)a, (const IT*)w, (OT*)out, M, N, K);
+        gemm_simple_kernel<IT, OT, true><<<grid, 256, 0, stream>>>((const IT*)a, (const IT*)w, (OT*)out, M, N, K, alpha);
       else
-        gemm_simple_kernel<IT, OT, false><<<grid, 256, 0, stream>>>((const IT*)a, (const IT*)w, (OT*)out, M, N, K);
+        gemm_simple_kernel<IT, OT, false><<<grid, 256, 0, stream>>>((const IT*)a, (const IT*)w, (OT*)out, M, N, K, alpha);
       return gb::check_launch("gemm_simple");
     });
   });

@@ -1,0 +1,171 @@
+// Routed experts, the plain kernels: a router that picks the `top` largest of E logits per token
+// and weighs them by a softmax over the chosen ones, each token's gate/up products against the
+// weights of its chosen experts, and the weighted sum of the experts' down products added into the
+// residual stream. 32-bit arithmetic; every output is a sum in a fixed order (over k within a
+// product, then over a token's choices in the router's order), so a token's result does not depend
+// on the rest of the batch.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_EXPERTS = 512;
+constexpr int MAX_TOP = 32;
+
+// One warp per token. z_e = h . W[e] + b[e] in 32-bit (the bias is 32-bit); the chosen experts in descending order of
+// their logit (the lower index first among equals); weights = softmax over the chosen logits.
+template <typename HT, typename WT>
+__global__ void __launch_bounds__(128)
+route_topk_kernel(const HT* __restrict__ h, const WT* __restrict__ w, const float* __restrict__ bias, int T, int E,
+                  int K, int top, int32_t* __restrict__ ids, float* __restrict__ weights) {
+  gb::pdl_launch_dependents();
+  gb::pdl_wait();
+  extern __shared__ float z_s[];       // [4][E]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= T) return;
+  float* z = z_s + warp * E;
+  const HT* hr = h + (size_t)t * K;
+  for (int e = 0; e < E; ++e) {
+    const WT* wr = w + (size_t)e * K;
+    float acc = 0.f;
+    for (int k = lane; k < K; k += 32) acc = fmaf(gb::to_float<HT>(hr[k]), gb::to_float<WT>(wr[k]), acc);
+    acc = gb::warp_sum(acc);
+    if (lane == 0) z[e] = acc + (bias ? bias[e] : 0.f);
+  }
+  __syncwarp();
+  // `top` rounds of a warp-wide arg-max; a chosen expert's logit is replaced by -inf
+  float chosen[MAX_TOP];
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < E; e += 32)
+      if (z[e] > best) { best = z[e]; at = e; }      // the first of equals within a lane
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    chosen[j] = best;
+    if (lane == 0) {
+      ids[(size_t)t * top + j] = at < E ? at : 0;
+      if (at < E) z[at] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  if (lane == 0) {
+    const float largest = chosen[0];
+    float sum = 0.f;
+    for (int j = 0; j < top; ++j) {
+      chosen[j] = expf(chosen[j] - largest);
+      sum += chosen[j];
+    }
+    for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] = chosen[j] / sum;
+  }
+}
+
+__device__ __forceinline__ float gate_act(int kind, float limit, float g, float u) {
+  if (kind == 1) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+  if (kind == 2) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return (g / (1.0f + expf(-1.702f * g))) * (u + 1.0f);
+  }
+  return (g / (1.0f + expf(-g))) * u;
+}
+
+// grid (T, top). act[(t * top + j)][f] = act(gate_e[f] . h_t, up_e[f] . h_t), e = ids[t][j]; the
+// expert's weights are [2F, K]: F gate rows, then F up rows. A warp per feature, lanes over k.
+template <typename HT, typename WT, typename OT>
+__global__ void __launch_bounds__(128)
+moe_gate_up_kernel(const HT* __restrict__ h, const WT* __restrict__ w, const int32_t* __restrict__ ids,
+                   OT* __restrict__ act, int top, int F, int K, int kind, float limit) {
+  extern __shared__ float h_s[];
+  const int t = blockIdx.x, j = blockIdx.y;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) h_s[k] = gb::to_float<HT>(h[(size_t)t * K + k]);
+  __syncthreads();
+  const int e = ids[(size_t)t * top + j];
+  const WT* we = w + (size_t)e * 2 * F * K;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int f = warp; f < F; f += 4) {
+    const WT* gr = we + (size_t)f * K;
+    const WT* ur = we + (size_t)(F + f) * K;
+    float g = 0.f, u = 0.f;
+    for (int k = lane; k < K; k += 32) {
+      g = fmaf(h_s[k], gb::to_float<WT>(gr[k]), g);
+      u = fmaf(h_s[k], gb::to_float<WT>(ur[k]), u);
+    }
+    g = gb::warp_sum(g);
+    u = gb::warp_sum(u);
+    if (lane == 0) act[((size_t)t * top + j) * F + f] = gb::from_float<OT>(gate_act(kind, limit, g, u));
+  }
+}
+
+// One block per token. x[t][n] += alpha * sum_j weights[t][j] * (down_e(j)[n] . act[t][j]).
+template <typename AT, typename WT>
+__global__ void __launch_bounds__(256)
+moe_down_kernel(const AT* __restrict__ act, const WT* __restrict__ w, const int32_t* __restrict__ ids,
+                const float* __restrict__ weights, float* __restrict__ x, int top, int F, int N, float alpha) {
+  extern __shared__ float a_s[];        // [top][F]
+  const int t = blockIdx.x;
+  for (int e = threadIdx.x; e < top * F; e += blockDim.x) a_s[e] = gb::to_float<AT>(act[(size_t)t * top * F + e]);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int n = warp; n < N; n += 8) {
+    float total = 0.f;
+    for (int j = 0; j < top; ++j) {
+      const int e = ids[(size_t)t * top + j];
+      const WT* wr = w + ((size_t)e * N + n) * F;
+      float acc = 0.f;
+      for (int f = lane; f < F; f += 32) acc = fmaf(a_s[j * F + f], gb::to_float<WT>(wr[f]), acc);
+      total = fmaf(weights[(size_t)t * top + j], gb::warp_sum(acc), total);
+    }
+    if (lane == 0) x[(size_t)t * N + n] = fmaf(alpha, total, x[(size_t)t * N + n]);
+  }
+}
+
+}  // namespace
+
+GB_EXPORT int gb_route_topk(const void* h, int h_dtype, const void* w, const float* bias, int w_dtype, int T, int E,
+                            int K, int top, int32_t* ids, float* weights, cudaStream_t stream) {
+  if (T <= 0) return GB_OK;
+  if (E < 1 || E > MAX_EXPERTS || top < 1 || top > MAX_TOP || top > E)
+    return gb::fail(GB_UNSUPPORTED, "route_topk: %d of %d experts (at most %d of %d)", top, E, MAX_TOP, MAX_EXPERTS);
+  return GB_DISPATCH_DTYPE(h_dtype, HT, [&]() -> int {
+    return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
+      return gb::check_pdl_launch(
+          gb::launch_pdl(route_topk_kernel<HT, WT>, dim3((T + 3) / 4), dim3(128), (size_t)4 * E * sizeof(float), stream,
+                         dim3(1, 1, 1), (const HT*)h, (const WT*)w, bias, T, E, K, top, ids, weights),
+          "route_topk");
+    });
+  });
+}
+
+GB_EXPORT int gb_moe_gate_up(const void* h, int h_dtype, const void* w, int w_dtype, const int32_t* ids, void* act,
+                             int act_dtype, int T, int top, int F, int K, int kind, float limit,
+                             cudaStream_t stream) {
+  if (T <= 0) return GB_OK;
+  if ((size_t)K * sizeof(float) > 48 * 1024) return gb::fail(GB_UNSUPPORTED, "moe_gate_up: width %d", K);
+  return GB_DISPATCH_DTYPE(h_dtype, HT, [&]() -> int {
+    return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
+      return GB_DISPATCH_DTYPE(act_dtype, OT, [&]() -> int {
+        moe_gate_up_kernel<HT, WT, OT><<<dim3(T, top), 128, (size_t)K * sizeof(float), stream>>>(
+            (const HT*)h, (const WT*)w, ids, (OT*)act, top, F, K, kind, limit);
+        return gb::check_launch("moe_gate_up");
+      });
+    });
+  });
+}
+
+GB_EXPORT int gb_moe_down(const void* act, int act_dtype, const void* w, int w_dtype, const int32_t* ids,
+                          const float* weights, float* x, int T, int top, int F, int N, float alpha,
+                          cudaStream_t stream) {
+  if (T <= 0) return GB_OK;
+  if ((size_t)top * F * sizeof(float) > 48 * 1024) return gb::fail(GB_UNSUPPORTED, "moe_down: %d x %d activations", top, F);
+  return GB_DISPATCH_DTYPE(act_dtype, AT, [&]() -> int {
+    return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
+      moe_down_kernel<AT, WT><<<T, 256, (size_t)top * F * sizeof(float), stream>>>(
+          (const AT*)act, (const WT*)w, ids, weights, x, top, F, N, alpha);
+      return gb::check_launch("moe_down");
+    });
+  });
+}

@@ -86,6 +86,7 @@ class CudaOps:
             raise KernelError("garuda_b200 needs a CUDA device: there is no CPU path")
         self.device = torch.device(device)
         self.core = load_kernel_lib("garuda_core")
+        self._mixers = None
         self._declare_core()
         # A word of pinned host memory that a kernel whose bounded wait ran out writes its code to (the
         # device reaches pinned host memory directly); ``failed_wait`` reads it without a copy.
@@ -115,7 +116,14 @@ class CudaOps:
         L = self.core
         L.gb_last_error.restype = ctypes.c_char_p
         sig = {
-            "gb_embedding": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+            "gb_embedding": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+            "gb_layernorm": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
+            "gb_residual_axpy": [c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
+            "gb_rms_add": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_int, c_int, c_void_p],
+            "gb_gelu_gather_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                                   c_int, c_int, c_void_p],
+            "gb_cast": [c_void_p, c_void_p, c_int, c_longlong, c_void_p],
+            "gb_gated_act": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
             "gb_rmsnorm": [c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
             "gb_rope_kv_append": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
@@ -124,10 +132,10 @@ class CudaOps:
             "gb_rope_table": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
             "gb_silu_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
             "gb_residual_add": [c_void_p, c_void_p, c_int, c_longlong, c_void_p],
-            "gb_gemm_simple": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+            "gb_gemm_simple": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
             "gb_attention_simple": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
-                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-                                    c_void_p],
+                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                    c_int, c_void_p],
             "gb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p],
             "gb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                           c_void_p],
@@ -138,6 +146,33 @@ class CudaOps:
             fn = getattr(L, name)
             fn.argtypes = argtypes
             fn.restype = c_int
+
+    @property
+    def mixers(self):
+        """The library of the latent-attention and routed-expert kernels, compiled and loaded when
+        a model first needs it."""
+        if self._mixers is None:
+            L = load_kernel_lib("garuda_mixers")
+            L.gb_last_error.restype = ctypes.c_char_p
+            for name, argtypes in self._MIXER_SIGNATURES.items():
+                fn = getattr(L, name)
+                fn.argtypes = argtypes
+                fn.restype = c_int
+            self._mixers = L
+        return self._mixers
+
+    _MIXER_SIGNATURES = {
+            "gb_latent_append": [c_void_p, c_int, c_void_p, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p,
+                                 c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
+            "gb_head_gemm": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_int,
+                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+            "gb_route_topk": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                              c_void_p, c_void_p],
+            "gb_moe_gate_up": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                               c_int, c_float, c_void_p],
+            "gb_moe_down": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                            c_float, c_void_p],
+    }
 
     def _stream(self):
         if self._held_stream is not None:
@@ -175,7 +210,8 @@ class CudaOps:
             self._inv_freq[rotary] = torch.from_numpy(rotary_frequencies(rotary)).to(self.device)
         return self._inv_freq[rotary]
 
-    def embedding(self, table, ids, out):
+    def embedding(self, table, ids, out, scale: float = 1.0):
+        """``out[t] = table[ids[t]] * scale`` in 32-bit."""
         self._on_device(table, ids, out)
         _need(out.dtype == torch.float32 and out.is_contiguous(), "embedding: out must be contiguous float32")
         _need(ids.dtype == torch.int32, "embedding: ids must be int32")
@@ -184,7 +220,7 @@ class CudaOps:
         _need(out.shape[0] >= T, "embedding: out has too few rows")
         self._check(self.core, self.core.gb_embedding(
             table.data_ptr(), _tag(table, "embedding table"), ids.data_ptr(), out.data_ptr(), T,
-            table.shape[1], table.shape[0], self._stream()), "embedding")
+            table.shape[1], table.shape[0], float(scale), self._stream()), "embedding")
 
     def rmsnorm(self, x, weight, eps, out, rows=None):
         self._on_device(x, weight, out, rows)
@@ -199,8 +235,9 @@ class CudaOps:
             x.data_ptr(), weight.data_ptr(), _tag(weight, "norm weight"), float(eps), out.data_ptr(),
             _tag(out, "rmsnorm out"), _ptr(rows), n, d, self._stream()), "rmsnorm")
 
-    def linear(self, a, w, out, accumulate: bool = False, ctx=None, emit_norm=None):
-        """``out[M,N] (+)= a[M,K] @ w[N,K]^T``; accumulation is into a 32-bit ``out``.
+    def linear(self, a, w, out, accumulate: bool = False, ctx=None, emit_norm=None, alpha: float = 1.0):
+        """``out[M,N] (+)= a[M,K] @ w[N,K]^T``; accumulation is into a 32-bit ``out``, as
+        ``out += alpha * product`` (``alpha``: a model's residual multiplier).
 
         ``emit_norm`` (with ``ctx``): the norm part that will be applied to ``out`` next. Where
         the kernel can, it folds that norm's first half into this product and returns a
@@ -214,13 +251,14 @@ class CudaOps:
             _need(False, f"linear: shapes {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)}")
         _need(a.dtype == w.dtype, "linear: a and w must have one dtype")
         _need(a.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "linear: operands must be contiguous")
+        _need(accumulate or alpha == 1.0, "linear: a multiplier goes with accumulation only")
         if self.tc is not None and a.dtype == torch.bfloat16:
-            pending = self._pending_for(ctx, emit_norm, out, accumulate)
-            if self.tc.linear(a, w, out, accumulate, emit=pending):
+            pending = self._pending_for(ctx, emit_norm, out, accumulate) if alpha == 1.0 else None
+            if self.tc.linear(a, w, out, accumulate, emit=pending, alpha=alpha):
                 return pending
         self._check(self.core, self.core.gb_gemm_simple(
             a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, _tag(a, "linear input"),
-            _tag(out, "linear output"), int(accumulate), self._stream()), "linear")
+            _tag(out, "linear output"), int(accumulate), float(alpha), self._stream()), "linear")
 
     def _pending_for(self, ctx, norm, x, accumulate):
         """A ``PendingNorm`` with buffers for the product that adds into ``x``, or None."""
@@ -387,24 +425,202 @@ class CudaOps:
             self.inv_freq(rotary).data_ptr(), int(rotary.interleaved), self._stream()), "rope_inplace")
 
     def paged_attention(self, q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out,
-                        scale, window, page_size, num_requests, max_q_len, max_kv_len, ws=None, min_q_len=1):
+                        scale, window, page_size, num_requests, max_q_len, max_kv_len, ws=None, min_q_len=1,
+                        value_dim=None):
+        """``value_dim``: how many of a value row's first channels are the value (``out`` is then
+        ``[T, Hq * value_dim]``); None: all ``hd``. A mixer whose keys and values are parts of one
+        cached row passes the same pool for both and the narrower width."""
         self._on_device(q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out)
         T, Hq, hd = q.shape
         Hkv = k_pool.shape[1]
-        _need(q.is_contiguous() and out.is_contiguous() and out.shape == (T, Hq * hd), "attention: q/out shape")
+        vd = hd if value_dim is None else int(value_dim)
+        _need(q.is_contiguous() and out.is_contiguous() and out.shape == (T, Hq * vd), "attention: q/out shape")
         _need(q.dtype == k_pool.dtype == v_pool.dtype == out.dtype, "attention: one dtype for q, cache and out")
         _need(tuple(k_pool.shape[1:]) == (Hkv, page_size, hd) and k_pool.shape == v_pool.shape,
               "attention: pool shape")
+        _need(0 < vd <= hd, "attention: value_dim must be within the row")
         _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attention: block table")
-        if self.tc is not None and q.dtype == torch.bfloat16 and self.tc.paged_attention(
+        if vd == hd and self.tc is not None and q.dtype == torch.bfloat16 and self.tc.paged_attention(
                 q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, scale, window, page_size,
                 num_requests, max_q_len, max_kv_len, ws, min_q_len):
             return
         self._check(self.core, self.core.gb_attention_simple(
             q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), _tag(q, "attention q"),
             block_table.data_ptr(), block_table.shape[1], cu_q.data_ptr(), kv_lens.data_ptr(),
-            token_req.data_ptr(), out.data_ptr(), T, Hq, Hkv, hd, float(scale), int(window),
+            token_req.data_ptr(), out.data_ptr(), T, Hq, Hkv, hd, hd, vd, float(scale), int(window),
             int(page_size), self._stream()), "attention")
+
+    # ------------------------------------------------------------------ more norms and residual forms
+    def layernorm(self, x, weight, bias, eps, out, rows=None):
+        """``(x - mean) / sqrt(var + eps) * weight + bias`` per row (``bias`` may be None), 32-bit
+        arithmetic, ``out`` in its own dtype; ``rows``: only these rows of ``x``."""
+        self._on_device(x, weight, bias, out, rows)
+        _need(x.dtype == torch.float32 and x.is_contiguous(), "layernorm: x must be contiguous float32")
+        d = x.shape[1]
+        _need(weight.numel() == d and out.shape[1] == d and out.is_contiguous(), "layernorm: widths differ")
+        _need(bias is None or (bias.numel() == d and bias.dtype == weight.dtype), "layernorm: bias")
+        n = x.shape[0] if rows is None else rows.shape[0]
+        _need(out.shape[0] == n, "layernorm: out has the wrong number of rows")
+        if rows is not None:
+            _need(rows.dtype == torch.int32, "layernorm: rows must be int32")
+        self._check(self.core, self.core.gb_layernorm(
+            x.data_ptr(), weight.data_ptr(), _ptr(bias), _tag(weight, "norm weight"), float(eps), out.data_ptr(),
+            _tag(out, "layernorm out"), _ptr(rows), n, d, self._stream()), "layernorm")
+
+    def residual_axpy(self, x, y=None, alpha: float = 1.0, row=None):
+        """``x[t] += alpha * y[t] + row`` on the 32-bit residual; ``y`` or ``row`` may be None."""
+        self._on_device(x, y, row)
+        _need(x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2, "residual_axpy: x must be float32 [T, d]")
+        T, d = x.shape
+        _need(y is None or (y.shape == x.shape and y.is_contiguous()), "residual_axpy: y must have x's shape")
+        _need(row is None or (row.numel() == d and row.is_contiguous()), "residual_axpy: row must be [d]")
+        if y is None and row is None:
+            return
+        self._check(self.core, self.core.gb_residual_axpy(
+            x.data_ptr(), _ptr(y), _tag(y, "residual_axpy y") if y is not None else GB_F32, float(alpha), _ptr(row),
+            _tag(row, "residual_axpy row") if row is not None else GB_F32, T, d, self._stream()), "residual_axpy")
+
+    def rms_add(self, x, y, weight, eps, alpha: float = 1.0):
+        """``x[t] += alpha * y[t] / sqrt(mean(y[t]^2) + eps) * weight`` (x, y 32-bit)."""
+        self._on_device(x, y, weight)
+        _need(x.dtype == torch.float32 and y.dtype == torch.float32 and x.shape == y.shape and x.is_contiguous()
+              and y.is_contiguous() and weight.numel() == x.shape[1], "rms_add: x and y float32 [T, d], weight [d]")
+        self._check(self.core, self.core.gb_rms_add(
+            x.data_ptr(), y.data_ptr(), weight.data_ptr(), _tag(weight, "rms_add weight"), float(eps), float(alpha),
+            x.shape[0], x.shape[1], self._stream()), "rms_add")
+
+    def gelu_gather_mul(self, z, table, ids, col0, out):
+        """``out[t, j] = gelu_tanh(z[t, j]) * table[ids[t], col0 + j]``."""
+        self._on_device(z, table, ids, out)
+        T, dim = out.shape
+        _need(z.shape == out.shape and z.is_contiguous() and out.is_contiguous() and table.is_contiguous()
+              and ids.dtype == torch.int32, "gelu_gather_mul: shapes")
+        self._check(self.core, self.core.gb_gelu_gather_mul(
+            z.data_ptr(), _tag(z, "z"), table.data_ptr(), _tag(table, "table"), table.shape[1], int(col0),
+            ids.data_ptr(), out.data_ptr(), _tag(out, "out"), T, dim, table.shape[0], self._stream()), "gelu_gather_mul")
+
+    def cast(self, x, out):
+        """``out = x`` rounded to ``out``'s dtype (x 32-bit)."""
+        self._on_device(x, out)
+        _need(x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and x.numel() == out.numel(),
+              "cast: float32 in, same size out")
+        self._check(self.core, self.core.gb_cast(x.data_ptr(), out.data_ptr(), _tag(out, "cast out"), x.numel(),
+                                                 self._stream()), "cast")
+
+    # ------------------------------------------------------------------ gated feed-forwards
+    GATE_ACTS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
+
+    def gated_act(self, gate_up, out, kind: str = "silu", limit: float = 0.0, group: int = 0):
+        """``out[M,F] = act(gate, up)``: ``silu(g) u``, ``gelu_tanh(g) u`` or, clamped,
+        ``g' sigmoid(1.702 g') (u' + 1)`` with ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)``.
+        ``gate_up`` rows are ``[gate | up]``, or with ``group`` 64 the layout of ``pack_gate_up``."""
+        self._on_device(gate_up, out)
+        M, F = out.shape
+        width = 2 * group * ((F + group - 1) // group) if group else 2 * F
+        _need(gate_up.shape == (M, width) and gate_up.is_contiguous() and out.is_contiguous(),
+              f"gated_act: gate_up must be [M, {width}] for out [M, {F}]")
+        self._check(self.core, self.core.gb_gated_act(
+            gate_up.data_ptr(), _tag(gate_up, "gated_act in"), out.data_ptr(), _tag(out, "gated_act out"),
+            M, F, group, width, self.GATE_ACTS[kind], float(limit), self._stream()), "gated_act")
+
+    def linear_gated(self, ctx, h, w_gate_up, act, kind: str = "silu", limit: float = 0.0):
+        """``act[M,F] = act(h @ gate^T, h @ up^T)``; ``w_gate_up`` from ``pack_gate_up``."""
+        if kind == "silu":
+            return self.linear_swiglu(ctx, h, w_gate_up, act)
+        M, F = act.shape
+        group = getattr(w_gate_up, "gb_group", 0)
+        h = self.normed(ctx, h)
+        if (group == 64 and self.tc is not None and h.dtype == torch.bfloat16
+                and self.tc.linear_swiglu(h, w_gate_up, act, kind=self.GATE_ACTS[kind], limit=limit)):
+            return
+        tmp = ctx.ws.get("gate_up", (M, w_gate_up.shape[0]), torch.float32)
+        self.linear(h, w_gate_up, tmp)
+        self.gated_act(tmp, act, kind, limit, group)
+
+    # ------------------------------------------------------------------ routed experts
+    def route_topk(self, h, w_router, bias, top, ids, weights):
+        """Router logits ``h @ w_router^T + bias`` in 32-bit; ``ids[T, top]`` the experts with the
+        largest logits (descending), ``weights[T, top]`` the softmax over those logits only."""
+        self._on_device(h, w_router, bias, ids, weights)
+        T, K = h.shape
+        E = w_router.shape[0]
+        _need(h.is_contiguous() and w_router.is_contiguous() and w_router.shape[1] == K, "route_topk: shapes")
+        _need(ids.dtype == torch.int32 and weights.dtype == torch.float32 and ids.shape == (T, top)
+              and weights.shape == (T, top) and ids.is_contiguous() and weights.is_contiguous(), "route_topk: outputs")
+        _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == E), "route_topk: a float32 bias")
+        self._check(self.mixers, self.mixers.gb_route_topk(
+            h.data_ptr(), _tag(h, "router input"), w_router.data_ptr(), _ptr(bias), _tag(w_router, "router"),
+            T, E, K, int(top), ids.data_ptr(), weights.data_ptr(), self._stream()), "route_topk")
+
+    def moe_gate_up(self, h, w_gate_up, ids, act, kind: str, limit: float):
+        """``act[T, top, F]``: every token's gate/up products against its chosen experts'
+        weights ``w_gate_up[E, 2F, K]`` (gate rows, then up rows), through the activation."""
+        self._on_device(h, w_gate_up, ids, act)
+        T, K = h.shape
+        top = ids.shape[1]
+        E, F2, _ = w_gate_up.shape
+        _need(h.is_contiguous() and w_gate_up.is_contiguous() and act.is_contiguous() and h.dtype == w_gate_up.dtype
+              and w_gate_up.shape[2] == K and act.shape == (T, top, F2 // 2), "moe_gate_up: shapes")
+        self._check(self.mixers, self.mixers.gb_moe_gate_up(
+            h.data_ptr(), _tag(h, "h"), w_gate_up.data_ptr(), _tag(w_gate_up, "w"), ids.data_ptr(), act.data_ptr(),
+            _tag(act, "act"), T, top, F2 // 2, K, self.GATE_ACTS[kind], float(limit), self._stream()), "moe_gate_up")
+
+    def moe_down(self, act, w_down, ids, weights, x, alpha: float = 1.0):
+        """``x[t] += alpha * sum_j weights[t, j] * (act[t, j] @ w_down[ids[t, j]]^T)``."""
+        self._on_device(act, w_down, ids, weights, x)
+        T, top, F = act.shape
+        E, N, _ = w_down.shape
+        _need(act.is_contiguous() and w_down.is_contiguous() and w_down.shape[2] == F and x.shape == (T, N)
+              and x.dtype == torch.float32 and x.is_contiguous(), "moe_down: shapes")
+        self._check(self.mixers, self.mixers.gb_moe_down(
+            act.data_ptr(), _tag(act, "act"), w_down.data_ptr(), _tag(w_down, "w"), ids.data_ptr(),
+            weights.data_ptr(), x.data_ptr(), T, top, F, N, float(alpha), self._stream()), "moe_down")
+
+    def routed_feed_forward(self, ctx, h, w_gate_up, w_down, ids, weights, x, kind: str, limit: float,
+                            alpha: float = 1.0):
+        """``x[t] += alpha * sum_j weights[t, j] * expert_{ids[t, j]}(h[t])`` with the experts'
+        weights stacked: ``w_gate_up [E, 2F, K]``, ``w_down [E, N, F]``."""
+        T, top = ids.shape
+        act = ctx.ws.get("expert_act", (T, top, w_down.shape[2]), h.dtype)
+        self.moe_gate_up(h, w_gate_up, ids, act, kind, limit)
+        self.moe_down(act, w_down, ids, weights, x, alpha)
+
+    # ------------------------------------------------------------------ attention over a cached latent
+    def latent_append(self, src, norm_w, eps, rank, rot, rotary, positions, token_req, block_table, pool, page_size):
+        """A step's cache rows ``[rms(src[:, :rank]) * norm_w | rotate(src[:, rank:rank + rot])]``
+        written to their pages. ``src``: 32-bit rows (a view with any row stride); ``rotary``: a
+        ``RotaryParams`` over the turned channels (pairs ``(2i, 2i + 1)``), or None."""
+        self._on_device(src, norm_w, positions, token_req, block_table, pool)
+        T = src.shape[0]
+        _need(src.dtype == torch.float32 and src.stride(1) == 1 and src.shape[1] == rank + rot, "latent_append: src")
+        _need(pool.is_contiguous() and tuple(pool.shape[1:]) == (1, page_size, rank + rot), "latent_append: pool shape")
+        _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "latent_append: block table")
+        inv, dims = None, 0
+        if rotary is not None:
+            _need(rotary.interleaved and rotary.head_dim <= rot, "latent_append: pairs (2i, 2i + 1) within the rotated part")
+            inv, dims = self.inv_freq(rotary), rotary.head_dim
+        self._check(self.mixers, self.mixers.gb_latent_append(
+            src.data_ptr(), src.stride(0), norm_w.data_ptr(), _tag(norm_w, "latent norm"), float(eps), int(rank),
+            int(rot), int(dims), _ptr(inv), positions.data_ptr(), token_req.data_ptr(), block_table.data_ptr(),
+            block_table.shape[1], int(page_size), pool.data_ptr(), _tag(pool, "latent pool"), T, self._stream()),
+            "latent_append")
+
+    def head_linear(self, a, w, out, n, k, transposed: bool, tail: int = 0):
+        """One small product per head: ``out[t, h, :n] = a[t, h, :k] @ w_h^T`` and
+        ``out[t, h, n:n + tail] = a[t, h, k:k + tail]``. ``a [T, H, >= k + tail]`` and ``out
+        [T, H, >= n + tail]`` may be views (unit stride along the last axis). ``w`` is contiguous:
+        ``[H * n, k]`` (``w_h`` = its rows ``h n ..``) or, ``transposed``, ``[H * k, n]`` (``w_h^T``
+        = its rows ``h k ..``: the product with the transposed per-head matrix)."""
+        self._on_device(a, w, out)
+        T, H = a.shape[0], a.shape[1]
+        _need(a.dim() == 3 and out.dim() == 3 and a.stride(2) == 1 and out.stride(2) == 1 and out.shape[:2] == (T, H)
+              and a.shape[2] >= k + tail and out.shape[2] >= n + tail, "head_linear: a and out are [T, H, *] views")
+        _need(w.is_contiguous() and tuple(w.shape) == ((H * k, n) if transposed else (H * n, k)), "head_linear: weight shape")
+        w_n, w_k = (1, n) if transposed else (k, 1)
+        self._check(self.mixers, self.mixers.gb_head_gemm(
+            a.data_ptr(), _tag(a, "a"), a.stride(0), a.stride(1), w.data_ptr(), _tag(w, "w"), n * k, w_n, w_k,
+            out.data_ptr(), _tag(out, "out"), out.stride(0), out.stride(1), T, H, int(n), int(k), int(tail),
+            self._stream()), "head_linear")
 
     # ------------------------------------------------------------------ sampling
     def argmax(self, logits, out):

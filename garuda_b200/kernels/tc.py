@@ -126,9 +126,11 @@ class TensorCoreKernels:
         self.ops._check(self.lib, code, "gemm_tc")
         return True
 
-    def linear(self, a, w, out, accumulate, emit=None) -> bool:
+    def linear(self, a, w, out, accumulate, emit=None, alpha: float = 1.0) -> bool:
         """``emit``: a ``PendingNorm`` whose values and sums this accumulating product fills."""
         if w.dtype != torch.bfloat16 or out.dtype not in (torch.float32, torch.bfloat16):
+            return False
+        if alpha != 1.0:
             return False
         fold = None
         if emit is not None:
@@ -161,12 +163,14 @@ class TensorCoreKernels:
             int(page_size), None if fold is None else ctypes.byref(fold), self.ops._stream())
         self.ops._check(self.lib, code, "gemm_tc_qkv")
 
-    def linear_swiglu(self, h, w_gate_up, act, pending=None) -> bool:
+    def linear_swiglu(self, h, w_gate_up, act, pending=None, kind: int = 0, limit: float = 0.0) -> bool:
         """``w_gate_up``: the packed layout of ``CudaOps.pack_gate_up``. ``pending``: the
         ``PendingNorm`` whose values ``h`` is."""
         F = act.shape[1]
         if (w_gate_up.dtype != torch.bfloat16 or act.dtype != torch.bfloat16
                 or w_gate_up.shape[0] != 128 * ((F + 63) // 64)):
+            return False
+        if kind != 0:
             return False
         return self._gemm(h, w_gate_up, act, F, 2, self._consume(pending))
 

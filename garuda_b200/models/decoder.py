@@ -15,8 +15,8 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..parts.base import (PartSpec, TensorSpec, PagedKV, FixedState, LayerCache, build_part,
-                          _REGISTRIES)
+from ..parts.base import (PartSpec, TensorSpec, PagedKV, PagedLatent, FixedState, LayerCache, build_part,
+                          tensor_name, _REGISTRIES)
 from ..parts.block import BlockSpec
 
 
@@ -24,9 +24,14 @@ from ..parts.block import BlockSpec
 class LayerCall:
     """One entry of the run order. ``layer`` indexes ``ModelSpec.layers``.
     ``reads_cache_of``: index of an earlier entry of the run order whose cache
-    this call reads (it then stores nothing itself)."""
+    this call reads (it then stores nothing itself). A model that runs a stretch of its layers
+    several times marks the first call of every pass: ``add_embedding`` adds the embedding's
+    output (the stream as it was before the first layer) to the stream before the call, and
+    ``add_row = (tensor, r)`` then adds row ``r`` of that model-level ``[rows, width]`` tensor."""
     layer: int
     reads_cache_of: Optional[int] = None
+    add_embedding: bool = False
+    add_row: Optional[Tuple[str, int]] = None
 
 
 @dataclass
@@ -41,6 +46,9 @@ class ModelSpec:
     final_norm: PartSpec
     head: Optional[str]                  # tensor name of the [vocab, width] head; None: tied
     embedding_init: Tuple = ("normal", 0.02)
+    embedding_scale: float = 1.0         # the embedding's output is the table's row times this
+    # tensors of the model itself that no part owns (what ``LayerCall.add_row`` names): name -> spec
+    extra_tensors: Optional[Dict[str, TensorSpec]] = None
     eos_token_ids: Tuple[int, ...] = ()  # generation ends on any of them (config.json may list several)
     # names a model folder may hold although the model reads nothing from them (a tied model's
     # stored copy of its head); anything else the model did not ask for is an error
@@ -84,7 +92,7 @@ class Decoder:
         for i, (call, need) in enumerate(zip(spec.order, self.call_need)):
             if call.reads_cache_of is not None or need is None:
                 continue
-            if isinstance(need, PagedKV):
+            if isinstance(need, (PagedKV, PagedLatent)):
                 groups.setdefault(need, []).append(i)
             elif isinstance(need, FixedState):
                 self.state_calls.append(i)
@@ -104,9 +112,10 @@ class Decoder:
         for block in self.blocks:
             for part, prefix in block.parts():
                 for local, ts in part.tensors().items():
-                    out[prefix + local] = ts
+                    out[tensor_name(prefix, local)] = ts
         for local, ts in self.final_norm.tensors().items():
-            out[s.final_norm.prefix + local] = ts
+            out[tensor_name(s.final_norm.prefix, local)] = ts
+        out.update(s.extra_tensors or {})
         if s.head is not None:
             out[s.head] = TensorSpec((s.vocab_size, s.width), init=s.embedding_init)
         return out
@@ -119,9 +128,11 @@ class Decoder:
         self.head = self.embedding if s.head is None else tensors[s.head]
         for block in self.blocks:
             for part, prefix in block.parts():
-                part.load({local: tensors[prefix + local] for local in part.tensors()}, ops, dtype)
-        self.final_norm.load({local: tensors[s.final_norm.prefix + local]
+                part.load({local: tensors[tensor_name(prefix, local)] for local in part.tensors()}, ops, dtype)
+        self.final_norm.load({local: tensors[tensor_name(s.final_norm.prefix, local)]
                               for local in self.final_norm.tensors()}, ops, dtype)
+        self.extra = {name: tensors[name] for name in (s.extra_tensors or {})}
+        self.keeps_embedding = any(call.add_embedding for call in s.order)
 
     # ---- one step ----------------------------------------------------------
     def forward(self, ctx, layer_caches: List[Optional[LayerCache]]) -> torch.Tensor:
@@ -130,11 +141,21 @@ class Decoder:
         and the head touch no other row (garuda/src/llama/mod.rs:1110-1113)."""
         b, ops, s = ctx.batch, self.ops, self.spec
         x = ctx.ws.get("residual", (b.num_tokens, s.width), torch.float32)
-        ops.embedding(self.embedding, b.token_ids, x)
+        if s.embedding_scale != 1.0:
+            ops.embedding(self.embedding, b.token_ids, x, s.embedding_scale)
+        else:
+            ops.embedding(self.embedding, b.token_ids, x)
+        x0 = None
+        if self.keeps_embedding:
+            x0 = ctx.ws.get("embedding_out", (b.num_tokens, s.width), torch.float32)
+            x0.copy_(x)
         # a layer's last product may fold in the first half of the next layer's norm
         pending = None
         for i, call in enumerate(s.order):
             block = self.blocks[call.layer]
+            if call.add_embedding or call.add_row is not None:
+                row = self.extra[call.add_row[0]][call.add_row[1]] if call.add_row is not None else None
+                ops.residual_axpy(x, x0 if call.add_embedding else None, 1.0, row)
             nxt = self.blocks[s.order[i + 1].layer] if i + 1 < len(s.order) else None
             takes = getattr(nxt, "takes_pending_norm", None)
             next_norm = takes(ops) if takes is not None else None

@@ -1,11 +1,14 @@
 """Parts a decoder is put together from. Importing the package registers the
 built-in ones."""
-from .base import (Part, Norm, PositionEncoding, Mixer, FeedForward, TensorSpec, PagedKV,
-                   FixedState, LayerCache, PartSpec, build_part, register_mixer,
+from .base import (Part, Norm, PositionEncoding, Mixer, FeedForward, ResidualBranch, TensorSpec, PagedKV,
+                   PagedLatent, FixedState, LayerCache, PartSpec, build_part, register_mixer,
                    register_feed_forward, register_norm, register_position_encoding,
-                   register_block)
-from .norm import RMSNorm
+                   register_block, register_branch)
+from .norm import RMSNorm, LayerNorm
 from .rotary import Rotary, NoPositions, RotaryParams
 from .attention import PagedAttention
-from .mlp import SwiGLU
+from .mlp import SwiGLU, GatedFeedForward
+from .latent_attention import LatentAttention
+from .experts import RoutedExperts
+from .token_side import TokenSide
 from .block import BlockSpec, PreNormBlock

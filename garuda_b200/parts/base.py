@@ -47,6 +47,16 @@ class PagedKV:
 
 
 @dataclass(frozen=True)
+class PagedLatent:
+    """A mixer that keeps one vector per position, shared by all its heads (a compressed
+    latent from which keys and values are computed, with whatever rides along: a rotated key
+    part). The pool is ``[num_pages, 1, page_size, width]`` and comes as ``LayerCache.k``;
+    there is no second pool. ``window`` as for ``PagedKV``."""
+    width: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
 class FixedState:
     """A mixer that keeps a state of fixed size per request
     (garuda/src/cache/mod.rs:630-648 is the reference's example)."""
@@ -87,6 +97,10 @@ class Part:
     #: holds, and allocate nothing. The built-in parts say True; a part that says nothing is run
     #: kernel by kernel.
     graph_safe = False
+    #: A mixer or feed-forward that says True takes ``alpha`` in ``forward`` and adds ``alpha *
+    #: output`` into the residual itself (a model's residual multiplier); for one that does not,
+    #: the block scales and adds what it returns.
+    scales_residual = False
 
     def tensors(self) -> Dict[str, TensorSpec]:
         return {}
@@ -136,12 +150,22 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class ResidualBranch(Part):
+    """Something a layer adds to the residual stream after its mixer and feed-forward, computed
+    from the stream itself and the step's tokens (a per-layer token embedding, gated): it reads
+    no norm of the block and keeps no cache."""
+
+    def forward(self, ctx, x: torch.Tensor, alpha: float = 1.0) -> None:
+        """Adds ``alpha * branch(x)`` into ``x`` (32-bit ``[T, d]``)."""
+        raise NotImplementedError
+
+
 # --------------------------------------------------------------------------
 # registries: name -> class
 # --------------------------------------------------------------------------
 
 _REGISTRIES: Dict[str, Dict[str, Callable]] = {
-    "mixer": {}, "feed_forward": {}, "norm": {}, "position_encoding": {}, "block": {},
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position_encoding": {}, "block": {}, "branch": {},
 }
 
 
@@ -157,15 +181,23 @@ def register_feed_forward(name, cls=None): return _register("feed_forward", name
 def register_norm(name, cls=None): return _register("norm", name, cls)
 def register_position_encoding(name, cls=None): return _register("position_encoding", name, cls)
 def register_block(name, cls=None): return _register("block", name, cls)
+def register_branch(name, cls=None): return _register("branch", name, cls)
 
 
 @dataclass(frozen=True)
 class PartSpec:
     """A part named as data: registry ``kind``, registered ``name``, constructor
-    parameters, and the prefix its tensor names get in the checkpoint."""
+    parameters, and the prefix its tensor names get in the checkpoint. A local tensor name that
+    starts with ``@`` is a name of the model's own, shared by parts of several layers: it takes no
+    prefix (``@side.embed`` is the checkpoint's ``side.embed``)."""
     name: str
     params: dict = field(default_factory=dict)
     prefix: str = ""
+
+
+def tensor_name(prefix: str, local: str) -> str:
+    """The checkpoint's name of a part's tensor."""
+    return local[1:] if local.startswith("@") else prefix + local
 
 
 def build_part(kind: str, spec: PartSpec):

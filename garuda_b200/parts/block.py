@@ -4,11 +4,15 @@
 ``x += mixer(norm1(x)); x += ffn(norm2(x))``, the residual stream ``x`` in
 32-bit throughout. A part may add into the residual itself (fused into its
 last matrix product); if it returns a tensor instead, the block adds it.
+
+Two things a model may add to that: a residual multiplier ``m`` (``x += m *
+mixer(...)``, likewise the feed-forward), and branches that run after the
+feed-forward and add to ``x`` from ``x`` itself (``parts.ResidualBranch``).
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional
+from typing import Optional, Tuple
 
 from .base import PartSpec, build_part, register_block
 
@@ -21,6 +25,8 @@ class BlockSpec:
     mixer_norm: PartSpec
     feed_forward_norm: Optional[PartSpec]
     arrangement: str = "pre_norm"
+    residual_mult: float = 1.0                 # x += residual_mult * part(norm(x))
+    branches: Tuple[PartSpec, ...] = ()        # after the feed-forward, in order
 
 
 @register_block("pre_norm")
@@ -32,6 +38,8 @@ class PreNormBlock:
         self.feed_forward = build_part("feed_forward", spec.feed_forward) if spec.feed_forward else None
         self.feed_forward_norm = (build_part("norm", spec.feed_forward_norm)
                                   if spec.feed_forward_norm else None)
+        self.branches = [build_part("branch", b) for b in spec.branches]
+        self.mult = float(spec.residual_mult)
 
     def parts(self):
         """(part, tensor-name prefix) pairs, for the loader."""
@@ -40,12 +48,13 @@ class PreNormBlock:
         if self.feed_forward is not None:
             out += [(self.feed_forward_norm, s.feed_forward_norm.prefix),
                     (self.feed_forward, s.feed_forward.prefix)]
+        out += [(b, bs.prefix) for b, bs in zip(self.branches, s.branches)]
         return out
 
     def takes_pending_norm(self, ops):
         """The norm part that the layer in front may fold into its last product (see
         ``forward``'s ``pending``), or None."""
-        if getattr(ops, "folds_norms", False) and getattr(self.mixer, "takes_pending_norm", False) \
+        if self.mult == 1.0 and getattr(ops, "folds_norms", False) and getattr(self.mixer, "takes_pending_norm", False) \
                 and hasattr(self.mixer_norm, "fold"):
             return self.mixer_norm
         return None
@@ -73,6 +82,8 @@ class PreNormBlock:
         if that layer takes such a result. Returns the pending norm for the next layer, or None.
         Parts that know nothing of this are run with the plain norms."""
         ops = ctx.ops
+        if self.mult != 1.0 or self.branches:
+            return self._forward_scaled(ctx, x, cache)
         folds = getattr(ops, "folds_norms", False)
         h = pending if pending is not None else self.mixer_norm.forward(ctx, x)
         ff = self.feed_forward
@@ -97,3 +108,27 @@ class PreNormBlock:
         if y2 is not None:
             ops.residual_add(x, y2)
         return self._take_pending(ctx, x, y2 is None and "emit_norm" in kw)
+
+    def _run(self, ctx, part, x, h, *cache):
+        """``x += mult * part(h)``: by the part itself if it takes the multiplier, else here."""
+        if part.scales_residual:
+            y = part.forward(ctx, h, *cache, residual=x, alpha=self.mult)
+            if y is not None:
+                ctx.ops.residual_axpy(x, y, self.mult)
+        else:
+            y = part.forward(ctx, h, *cache)
+            if y is None:
+                raise RuntimeError(f"{type(part).__name__} returned nothing although it was given no residual to add to")
+            ctx.ops.residual_axpy(x, y, self.mult)
+
+    def _forward_scaled(self, ctx, x, cache):
+        """The block of a model with a residual multiplier or with branches: plain norms (nothing
+        is folded across parts), every part's output scaled as it is added."""
+        ctx.pending_norm = None
+        self._run(ctx, self.mixer, x, self.mixer_norm.forward(ctx, x), cache)
+        if self.feed_forward is not None:
+            self._run(ctx, self.feed_forward, x, self.feed_forward_norm.forward(ctx, x))
+        for branch in self.branches:
+            branch.forward(ctx, x, self.mult)
+        ctx.pending_norm = None
+        return None

@@ -1,0 +1,114 @@
+"""Causal attention whose keys and values are linear maps of one cached latent
+vector per position.
+
+Per position ``j`` the mixer caches ``[c_j | r_j]``: ``c_j`` the first ``rank``
+outputs of the down projection, RMS-normed with a weight; ``r_j`` its last
+``rot_dim`` outputs, rotated at position ``j`` (one rotated key part for all
+heads). Head ``h`` has an unrotated query part ``q^n`` (``dim`` wide) and a
+rotated one ``q^r``; its key at ``j`` is ``[W_uk,h c_j | r_j]`` and its value
+``W_uv,h c_j``:
+
+    s_ij = (q^n_i . W_uk,h c_j + q^r_i . r_j) * scale
+         = ((W_uk,h^T q^n_i) . c_j + q^r_i . r_j) * scale
+    o_i  = W_uv,h sum_j softmax_j(s_ij) c_j
+
+so the query is mapped through ``W_uk^T`` once, attention runs over the cached
+rows with all heads reading the same row (as paged attention with one key/value
+head whose values are the first ``rank`` channels of its keys), and ``W_uv``
+is applied to the result: per token the work on the cache is one pass over
+``rank + rot_dim`` numbers per position, whatever the number of heads.
+
+The rotation turns pairs ``(2i, 2i + 1)`` of the first ``rot_dims`` channels of
+the rotated parts by ``pos * base^(-2i / rot_dims)``; angles are 32-bit.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import numpy as np
+import torch
+
+from .base import Mixer, PagedLatent, TensorSpec, register_mixer
+from .rotary import RotaryParams
+
+
+@register_mixer("latent_attention")
+class LatentAttention(Mixer):
+    graph_safe = True
+    scales_residual = True
+
+    def __init__(self, width: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, scale: float,
+                 eps: float, rot_base: float = 10000.0, rot_dims: Optional[int] = None,
+                 window: Optional[int] = None, init_std: float = 0.02,
+                 names=("q", "dkv", "dkv.norm", "uk", "uv", "o")):
+        self.width, self.heads, self.dim, self.rot_dim = int(width), int(heads), int(dim), int(rot_dim)
+        self.vdim, self.rank = int(vdim), int(kv_rank)
+        self.scale, self.eps = float(scale), float(eps)
+        self.window = int(window) if window else None
+        dims = self.rot_dim if rot_dims is None else int(rot_dims)
+        if dims % 2 or not 0 <= dims <= self.rot_dim:
+            raise ValueError(f"the rotation turns an even number of at most {self.rot_dim} channels, got {dims}")
+        if min(self.heads, self.dim, self.vdim, self.rank) < 1 or self.rot_dim < 0:
+            raise ValueError("latent attention needs positive sizes")
+        self.rot_dims = dims
+        self.init_std = float(init_std)
+        self.names = tuple(names)
+        self.rotary = None
+        if dims:
+            # one frequency per pair, base^(-2i/dims), taken in 64-bit and rounded once
+            i = np.arange(dims // 2, dtype=np.float64)
+            freqs = np.power(float(rot_base), -2.0 * i / dims).astype(np.float32)
+            self.rotary = RotaryParams(float(rot_base), dims, True, tuple(float(f) for f in freqs))
+        self.q_width = self.heads * (self.dim + self.rot_dim)
+        self.row = self.rank + self.rot_dim
+
+    def tensors(self):
+        init = ("normal", self.init_std)
+        q, dkv, norm, uk, uv, o = self.names
+        return {q: TensorSpec((self.q_width, self.width), init=init),
+                dkv: TensorSpec((self.row, self.width), init=init),
+                norm: TensorSpec((self.rank,), role="vector", init=("ones",)),
+                uk: TensorSpec((self.heads * self.dim, self.rank), init=init),
+                uv: TensorSpec((self.heads * self.vdim, self.rank), init=init),
+                o: TensorSpec((self.width, self.heads * self.vdim), init=init)}
+
+    def cache_need(self):
+        return PagedLatent(self.row, self.window)
+
+    def load(self, tensors, ops, dtype):
+        super().load(tensors, ops, dtype)
+        q, dkv, norm, uk, uv, o = self.names
+        # the query and the down projection are one product against their rows stacked
+        self.w_qd = torch.cat([tensors[q], tensors[dkv]], dim=0).contiguous()
+        self.norm_w = tensors[norm]
+        self.w_uk = tensors[uk].contiguous()
+        self.w_uv = tensors[uv].contiguous()
+        self.w_o = tensors[o].contiguous()
+
+    def forward(self, ctx, h, cache, residual=None, alpha: float = 1.0):
+        b, ops, ws = ctx.batch, self.ops, ctx.ws
+        T, H = h.shape[0], self.heads
+        qd = ws.get("latent_qd", (T, self.q_width + self.row), torch.float32)
+        ops.linear(h, self.w_qd, qd)
+        qv = qd[:, :self.q_width].unflatten(1, (H, self.dim + self.rot_dim))
+        if self.rotary is not None:
+            ops.rope_inplace(qv[..., self.dim:self.dim + self.rot_dims], b.positions, self.rotary)
+        if cache.writes:
+            ops.latent_append(qd[:, self.q_width:], self.norm_w, self.eps, self.rank, self.rot_dim, self.rotary,
+                              b.positions, b.token_req, cache.block_table, cache.k, cache.page_size)
+        # the query in the latent's coordinates: [W_uk^T q^n | q^r]
+        q_lat = ws.get("latent_q", (T, H, self.row), self.dtype)
+        ops.head_linear(qv, self.w_uk, q_lat, n=self.rank, k=self.dim, transposed=True, tail=self.rot_dim)
+        mixed = ws.get("latent_ctx", (T, H * self.rank), self.dtype)
+        ops.paged_attention(q_lat, cache.k, cache.k, cache.block_table, b.cu_q, b.kv_lens, b.token_req, mixed,
+                            self.scale, self.window or 0, cache.page_size, b.num_requests, b.max_q_len,
+                            b.max_kv_len, ws=ws, min_q_len=b.min_q_len, value_dim=self.rank)
+        out = ws.get("attn_ctx", (T, H * self.vdim), self.dtype)
+        ops.head_linear(mixed.unflatten(1, (H, self.rank)), self.w_uv, out.unflatten(1, (H, self.vdim)),
+                        n=self.vdim, k=self.rank, transposed=False)
+        if residual is not None:
+            ops.linear(out, self.w_o, residual, accumulate=True, alpha=alpha)
+            return None
+        y = ws.get("mixer_out", (T, self.width), torch.float32)
+        ops.linear(out, self.w_o, y)
+        return y

@@ -51,3 +51,46 @@ class SwiGLU(FeedForward):
         y = ctx.ws.get("ffn_out", (T, self.width), torch.float32)
         self.ops.linear(act, self.w_down, y)
         return y
+
+
+@register_feed_forward("gated")
+class GatedFeedForward(FeedForward):
+    """``down(act(gate h, up h))`` with the activation and the tensors' names as parameters:
+    ``activation`` is ``"silu"`` (``silu(g) u``), ``"gelu_tanh"`` (``gelu_tanh(g) u``) or
+    ``"clamped_swish"`` (``g' sigmoid(1.702 g') (u' + 1)`` with ``g' = min(g, limit)`` and
+    ``u' = clamp(u, -limit, limit)``). The activation is 32-bit on the 32-bit accumulators.
+    The last product adds ``alpha * output`` into the residual."""
+    graph_safe = True
+    scales_residual = True
+
+    def __init__(self, width: int, inner: int, activation: str = "silu", limit: float = 0.0,
+                 names=("gate", "up", "down"), init_std: float = 0.02):
+        if activation not in ("silu", "gelu_tanh", "clamped_swish"):
+            raise ValueError(f"unknown gated activation {activation!r}")
+        self.width, self.inner = int(width), int(inner)
+        self.activation, self.limit = activation, float(limit)
+        self.names = tuple(names)
+        self.init_std = float(init_std)
+
+    def tensors(self):
+        init = ("normal", self.init_std)
+        g, u, d = self.names
+        return {g: TensorSpec((self.inner, self.width), init=init), u: TensorSpec((self.inner, self.width), init=init),
+                d: TensorSpec((self.width, self.inner), init=init)}
+
+    def load(self, tensors, ops, dtype):
+        super().load(tensors, ops, dtype)
+        g, u, d = self.names
+        self.w_gate_up = ops.pack_gate_up(tensors[g], tensors[u])
+        self.w_down = tensors[d].contiguous()
+
+    def forward(self, ctx, h, residual=None, alpha: float = 1.0):
+        T = h.shape[0]
+        act = ctx.ws.get("ffn_act", (T, self.inner), self.dtype)
+        self.ops.linear_gated(ctx, h, self.w_gate_up, act, self.activation, self.limit)
+        if residual is not None:
+            self.ops.linear(act, self.w_down, residual, accumulate=True, alpha=alpha)
+            return None
+        y = ctx.ws.get("ffn_out", (T, self.width), torch.float32)
+        self.ops.linear(act, self.w_down, y)
+        return y

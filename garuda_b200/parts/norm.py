@@ -1,4 +1,5 @@
-"""RMS norm: ``x * 1/sqrt(mean(x^2) + eps) * weight``.
+"""RMS norm: ``x * 1/sqrt(mean(x^2) + eps) * weight``, and layer norm:
+``(x - mean) / sqrt(var + eps) * weight + bias``.
 
 garuda/src/simd/mod.rs:166-173 (eps inside the root, added to the mean) and
 garuda/src/llama/mod.rs:733-738 (scale, then a plain multiply by the weight).
@@ -42,4 +43,36 @@ class RMSNorm(Norm):
         n = x.shape[0] if rows is None else rows.shape[0]
         out = ctx.ws.get(out_name, (n, self.width), self.dtype)
         self.ops.rmsnorm(x, self.weight, self.eps, out, rows)
+        return out
+
+
+@register_norm("layer")
+class LayerNorm(Norm):
+    """``(x - mean) / sqrt(var + eps) * weight + bias`` with ``var`` the mean of the squared
+    deviations; 32-bit in the kernel, the result rounded to the compute dtype. ``weight_name``
+    and ``bias_name`` are the tensors' local names (``bias_name`` None: no bias)."""
+    graph_safe = True
+
+    def __init__(self, width: int, eps: float, weight_name: str = "weight", bias_name: Optional[str] = "bias",
+                 weight_init=("ones",)):
+        self.width, self.eps = int(width), float(eps)
+        self.weight_name, self.bias_name = weight_name, bias_name
+        self.weight_init = tuple(weight_init)
+
+    def tensors(self):
+        t = {self.weight_name: TensorSpec((self.width,), role="vector", init=self.weight_init)}
+        if self.bias_name is not None:
+            t[self.bias_name] = TensorSpec((self.width,), role="vector", init=("normal", 0.02))
+        return t
+
+    def load(self, tensors, ops, dtype):
+        super().load(tensors, ops, dtype)
+        self.weight = tensors[self.weight_name]
+        self.bias = tensors[self.bias_name] if self.bias_name is not None else None
+
+    def forward(self, ctx, x: torch.Tensor, rows: Optional[torch.Tensor] = None,
+                out_name: str = "normed") -> torch.Tensor:
+        n = x.shape[0] if rows is None else rows.shape[0]
+        out = ctx.ws.get(out_name, (n, self.width), self.dtype)
+        self.ops.layernorm(x, self.weight, self.bias, self.eps, out, rows)
         return out

@@ -26,8 +26,8 @@ class CpuOps:
         self.tc = None
 
     # garuda/src/llama/mod.rs:198-200, :1078-1085
-    def embedding(self, table, ids, out):
-        out[: ids.shape[0]] = table[ids.long()].float()
+    def embedding(self, table, ids, out, scale=1.0):
+        out[: ids.shape[0]] = table[ids.long()].float() * scale
 
     # garuda/src/simd/mod.rs:166-173; garuda/src/llama/mod.rs:733-738
     def rmsnorm(self, x, weight, eps, out, rows=None):
@@ -36,10 +36,10 @@ class CpuOps:
         out.copy_(((xs * (1.0 / torch.sqrt(ms + eps))) * weight.float()).to(out.dtype))
 
     # garuda/src/simd/mod.rs:96-129
-    def linear(self, a, w, out, accumulate=False):
+    def linear(self, a, w, out, accumulate=False, alpha=1.0):
         y = a.float() @ w.float().t()
         if accumulate:
-            out += y
+            out += alpha * y
         else:
             out.copy_(y.to(out.dtype))
 
@@ -119,11 +119,13 @@ class CpuOps:
 
     # garuda/src/llama/mod.rs:793-818; garuda/src/cache/mod.rs:333-338
     def paged_attention(self, q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out,
-                        scale, window, page_size, num_requests, max_q_len, max_kv_len, ws=None, min_q_len=1):
+                        scale, window, page_size, num_requests, max_q_len, max_kv_len, ws=None, min_q_len=1,
+                        value_dim=None):
         T, Hq, hd = q.shape
         Hkv = k_pool.shape[1]
         g = Hq // Hkv
-        res = torch.zeros(T, Hq, hd)
+        vd = hd if value_dim is None else value_dim
+        res = torch.zeros(T, Hq, vd)
         for t in range(T):
             r = int(token_req[t])
             q_len = int(cu_q[r + 1] - cu_q[r])
@@ -133,12 +135,114 @@ class CpuOps:
             pages = block_table[r, (js // page_size)].long()
             assert (pages >= 0).all(), "attention reads a position whose page was given back"
             K = k_pool[pages, :, (js % page_size), :].float()    # [n, Hkv, hd]
-            V = v_pool[pages, :, (js % page_size), :].float()
+            V = v_pool[pages, :, (js % page_size), :vd].float()
             for h in range(Hq):
                 s = (K[:, h // g, :] @ q[t, h].float()) * scale
                 p = torch.softmax(s, 0)
                 res[t, h] = p @ V[:, h // g, :]
-        out.copy_(res.reshape(T, Hq * hd).to(out.dtype))
+        out.copy_(res.reshape(T, Hq * vd).to(out.dtype))
+
+    # ---- parts the reference has no counterpart of: each is the formula in its docstring ----
+    def layernorm(self, x, weight, bias, eps, out, rows=None):
+        """(x - mean) / sqrt(var + eps) * w + b, var = mean of squared deviations"""
+        xs = x if rows is None else x[rows.long()]
+        mu = xs.mean(-1, keepdim=True)
+        var = ((xs - mu) ** 2).mean(-1, keepdim=True)
+        y = (xs - mu) / torch.sqrt(var + eps) * weight.float()
+        if bias is not None:
+            y = y + bias.float()
+        out.copy_(y.to(out.dtype))
+
+    def residual_axpy(self, x, y=None, alpha=1.0, row=None):
+        if y is not None:
+            x += alpha * y.float()
+        if row is not None:
+            x += row.float()[None, :]
+
+    def rms_add(self, x, y, weight, eps, alpha=1.0):
+        """x += alpha * y / sqrt(mean(y^2) + eps) * w"""
+        x += alpha * (y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps)) * weight.float()
+
+    @staticmethod
+    def _gelu_tanh(z):
+        return 0.5 * z * (1.0 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
+
+    def gelu_gather_mul(self, z, table, ids, col0, out):
+        e = table[ids.long(), col0:col0 + out.shape[1]].float()
+        out.copy_((self._gelu_tanh(z.float()) * e).to(out.dtype))
+
+    def cast(self, x, out):
+        out.copy_(x.to(out.dtype))
+
+    def gated_act(self, gate_up, out, kind="silu", limit=0.0, group=0):
+        F = out.shape[1]
+        g, u = gate_up[:, :F].float(), gate_up[:, F:].float()
+        if kind == "silu":
+            y = g / (1.0 + torch.exp(-g)) * u
+        elif kind == "gelu_tanh":
+            y = self._gelu_tanh(g) * u
+        else:
+            g = torch.clamp(g, max=limit)
+            u = torch.clamp(u, -limit, limit)
+            y = g / (1.0 + torch.exp(-1.702 * g)) * (u + 1.0)
+        out.copy_(y.to(out.dtype))
+
+    def linear_gated(self, ctx, h, w_gate_up, act, kind="silu", limit=0.0):
+        self.gated_act(h.float() @ w_gate_up.float().t(), act, kind, limit)
+
+    def route_topk(self, h, w_router, bias, top, ids, weights):
+        z = h.float() @ w_router.float().t()
+        if bias is not None:
+            z = z + bias.float()
+        order = torch.sort(-z, dim=-1, stable=True).indices[:, :top]
+        ids.copy_(order.to(torch.int32))
+        weights.copy_(torch.softmax(torch.gather(z, 1, order), -1))
+
+    def moe_gate_up(self, h, w_gate_up, ids, act, kind, limit):
+        T, top = ids.shape
+        F = act.shape[2]
+        for t in range(T):
+            for j in range(top):
+                gu = (w_gate_up[int(ids[t, j])].float() @ h[t].float())[None, :]
+                self.gated_act(gu, act[t, j][None, :], kind, limit)
+
+    def moe_down(self, act, w_down, ids, weights, x, alpha=1.0):
+        T, top, F = act.shape
+        for t in range(T):
+            total = torch.zeros(x.shape[1])
+            for j in range(top):
+                total += weights[t, j] * (w_down[int(ids[t, j])].float() @ act[t, j].float())
+            x[t] += alpha * total
+
+    def routed_feed_forward(self, ctx, h, w_gate_up, w_down, ids, weights, x, kind, limit, alpha=1.0):
+        T, top = ids.shape
+        act = torch.zeros(T, top, w_down.shape[2], dtype=h.dtype)
+        self.moe_gate_up(h, w_gate_up, ids, act, kind, limit)
+        self.moe_down(act, w_down, ids, weights, x, alpha)
+
+    def latent_append(self, src, norm_w, eps, rank, rot, rotary, positions, token_req, block_table, pool, page_size):
+        """rows [rms(src[:, :rank]) * w | rotate(src[:, rank:])] into their pages"""
+        c = src[:, :rank]
+        c = c / torch.sqrt((c * c).mean(-1, keepdim=True) + eps) * norm_w.float()
+        r = src[:, rank:rank + rot].clone()
+        if rotary is not None:
+            d = rotary.head_dim
+            r[:, :d] = self._rotate(r[:, None, :d], positions, rotary)[:, 0]
+        row = torch.cat([c, r], -1)
+        for t in range(src.shape[0]):
+            pos = int(positions[t])
+            page = int(block_table[int(token_req[t]), pos // page_size])
+            if page >= 0:
+                pool[page, 0, pos % page_size, :] = row[t].to(pool.dtype)
+
+    def head_linear(self, a, w, out, n, k, transposed, tail=0):
+        T, H = a.shape[:2]
+        wf = w.float()
+        for h in range(H):
+            wh = wf[h * k:(h + 1) * k].t() if transposed else wf[h * n:(h + 1) * n]      # [n, k]
+            out[:, h, :n] = (a[:, h, :k].float() @ wh.t()).to(out.dtype)
+            if tail:
+                out[:, h, n:n + tail] = a[:, h, k:k + tail].to(out.dtype)
 
     # garuda/src/runtime/mod.rs:99-107
     def argmax(self, logits, out):
