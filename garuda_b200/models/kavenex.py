@@ -63,10 +63,17 @@ def kavenex_spec(cfg: KavenexConfig) -> ModelSpec:
                 order.append(LayerCall(i, add_embedding=first and t > 0, add_row=(STEP_TABLE, t) if first else None))
         order += [LayerCall(i) for i in range(stop, n)]
         extra[STEP_TABLE] = TensorSpec((times, cfg.width), role="vector", init=("normal", 0.02))
+    # what a folder may carry although this model reads nothing from it: tensors of mechanisms
+    # that its configuration leaves out
+    ignored = [f"l{i}.norm2{b}" for i, layer in enumerate(cfg.layers) if layer.mlp is None for b in ("", ".b")]
+    if cfg.loop is None:
+        ignored.append(STEP_TABLE)
+    if not cfg.side_dim:
+        ignored += [SIDE_TABLE] + [f"l{i}.side.{t}" for i in range(n) for t in ("gate", "proj", "norm")]
     return ModelSpec(
         architecture=cfg.architecture, width=cfg.width, vocab_size=cfg.vocab, max_positions=cfg.max_positions,
         embedding="embed", layers=layers, order=order, final_norm=_norm(cfg, "", "final.norm"), head="head",
-        embedding_scale=cfg.embedding_scale, eos_token_ids=cfg.eos_token_ids, extra_tensors=extra or None)
+        embedding_scale=cfg.embedding_scale, eos_token_ids=cfg.eos_token_ids, extra_tensors=extra or None, ignored_tensors=tuple(ignored))
 
 
 register_architecture("Kavenex", KavenexConfig.from_dict, kavenex_spec)

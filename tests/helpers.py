@@ -149,7 +149,8 @@ class TraceRunner:
              "--max-tokens", str(max_tokens), *extra],
             stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
         self.step_no = 0
-        self.vocab = json.load(open(os.path.join(model, "config.json")))["vocab_size"]
+        cfg = json.load(open(os.path.join(model, "config.json")))
+        self.vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
 
     def step(self, entries, end=()):
         """entries: list of (id, tokens, want). Returns logits [wanted, vocab] or None."""

@@ -50,9 +50,10 @@ def rotate_pairs(v, positions, base, dims):
     return out
 
 
-def latent_attention(h, w, p, mx, eps, positions):
+def latent_attention(h, w, p, mx, eps, positions, weights_out=None):
     """``mx``: the mixer's sizes. Keys and values of every head come from one latent vector per
-    position (``kv_rank`` wide, RMS-normed) and one rotated key part shared by the heads."""
+    position (``kv_rank`` wide, RMS-normed) and one rotated key part shared by the heads.
+    ``weights_out``: a list that receives every head's ``[T, T]`` attention weights."""
     T = h.shape[0]
     H, dn, dr, dv, rank = mx["heads"], mx["dim"], mx["rot_dim"], mx["vdim"], mx["kv_rank"]
     q = (h @ w[p + "q"].T).reshape(T, H, dn + dr)
@@ -71,6 +72,8 @@ def latent_attention(h, w, p, mx, eps, positions):
         s = np.where(np.tril(np.ones((T, T), dtype=bool)), s, -np.inf)
         s = s - s.max(-1, keepdims=True)
         e = np.exp(s)
+        if weights_out is not None:
+            weights_out.append(e / e.sum(-1, keepdims=True))
         out[:, hd] = (e / e.sum(-1, keepdims=True)) @ v[:, hd]
     return out.reshape(T, H * dv) @ w[p + "o"].T
 
