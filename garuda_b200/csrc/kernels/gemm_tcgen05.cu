@@ -92,7 +92,15 @@ struct EpilogueArgs {
   // CTAs ask for those weights to be brought into L2 meanwhile, each a slice.
   const uint8_t* next_stream;
   long long next_bytes;
+  // out += alpha * product for the accumulating epilogues (a model's residual multiplier)
+  float alpha = 1.0f;
+  // the gated epilogue's activation: GATE_SILU silu(g) u; GATE_GELU_TANH gelu_tanh(g) u;
+  // GATE_CLAMPED_SWISH g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit)
+  int gate_act = 0;
+  float gate_limit = 0.f;
 };
+
+enum GateAct : int { GATE_SILU = 0, GATE_GELU_TANH = 1, GATE_CLAMPED_SWISH = 2 };
 
 // This CTA's slice of `bytes` at `base` into L2 (cta of ctas; 16-byte granules), by one thread.
 __device__ __forceinline__ void prefetch_slice_l2(const uint8_t* base, long long bytes, int cta, int ctas) {
@@ -192,6 +200,20 @@ __device__ __forceinline__ void store_value<__nv_bfloat16>(__nv_bfloat16* p, flo
 // (about 2 ulp of a float) is far below the rounding of the bfloat16 result.
 __device__ __forceinline__ float silu_gate_fast(float g, float u) {
   return g * __frcp_rn(1.0f + __expf(-g)) * u;
+}
+
+// The gated epilogues' activation, chosen at run time (uniform over the launch). tanh through the
+// fast exponential: tanh(z) = 1 - 2 / (exp(2 z) + 1), which is exact at both ends.
+__device__ __forceinline__ float gate_fast(const EpilogueArgs& ra, float g, float u) {
+  if (ra.gate_act == GATE_SILU) return silu_gate_fast(g, u);
+  if (ra.gate_act == GATE_GELU_TANH) {
+    const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    const float th = 1.0f - 2.0f * __frcp_rn(__expf(2.0f * z) + 1.0f);
+    return 0.5f * g * (1.0f + th) * u;
+  }
+  g = fminf(g, ra.gate_limit);
+  u = fminf(fmaxf(u, -ra.gate_limit), ra.gate_limit);
+  return g * __frcp_rn(1.0f + __expf(-1.702f * g)) * (u + 1.0f);
 }
 
 // Sums each of sixteen values over the lanes of a warp with sixteen shuffles: at every step a
@@ -553,7 +575,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
               for (int j = 0; j < 16; ++j) {
                 const int col = n0 + c + j;      // token
                 if (col < rows_n)
-                  store_value<OT>(out + (size_t)col * ldo + feature, silu_gate_fast(v[j], xch[j * 64 + row_in_tile]));
+                  store_value<OT>(out + (size_t)col * ldo + feature, gate_fast(ra, v[j], xch[j * 64 + row_in_tile]));
               }
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");      // before the next chunk reuses the buffer
@@ -598,7 +620,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
               sq[j] = 0.f;
               if (row >= rows_m || col >= rows_n) continue;
               float x = v[j];
-              if (ADD) x += old[ADD ? q * 16 + j : 0];
+              if (ADD) x = fmaf(ra.alpha, x, old[ADD ? q * 16 + j : 0]);
               store_value<OT>(out + (size_t)col * ldo + row, x);
               if (emit) {
                 ra.h_out[(size_t)col * ldo + row] = __float2bfloat16_rn(x * w_row);
@@ -755,7 +777,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
 #pragma unroll
       for (int rr = 0; rr < 32; ++rr) {
         float v = turn[rr * 33 + lane];
-        if (ACC) v += old_cur[ACC ? rr : 0];
+        if (ACC) v = fmaf(ra.alpha, v, old_cur[ACC ? rr : 0]);
         if (rr < rows_valid) store_value<OT>(gbase + (size_t)rr * ldo + c, v);
         if (EMIT) {
           // the squares go back the way the values came: each lane then adds up its own token's
@@ -792,7 +814,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
           float v[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j)
-            v[j] = silu_gate_fast(__uint_as_float(g_[h * 16 + j]) * inv, __uint_as_float(u_[h * 16 + j]) * inv);
+            v[j] = gate_fast(ra, __uint_as_float(g_[h * 16 + j]) * inv, __uint_as_float(u_[h * 16 + j]) * inv);
           epilogue_store16<OT>(prow + q * 64 + c + h * 16, v, true);
         }
       }
@@ -873,7 +895,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
         if (row >= rows_m || col >= rows_n) continue;
         float v[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = silu_gate_fast(__uint_as_float(r0[j]) * inv, __uint_as_float(r1[j]) * inv);
+        for (int j = 0; j < 16; ++j) v[j] = gate_fast(ra, __uint_as_float(r0[j]) * inv, __uint_as_float(r1[j]) * inv);
         OT* p = out + (size_t)row * ldo + col;
         if (col + 16 <= rows_n) {
           epilogue_store16<OT>(p, v, vec);
@@ -897,7 +919,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
     OT* p = out + (size_t)row * ldo + col;
     if (EMIT) {
       for (int j = 0; j < 16 && col + j < rows_n; ++j) {
-        const float x = v[j] + gb::to_float<OT>(p[j]);
+        const float x = fmaf(ra.alpha, v[j], gb::to_float<OT>(p[j]));
         store_value<OT>(p + j, x);
         ra.h_out[(size_t)row * ldo + col + j] = __float2bfloat16_rn(x * ra.weight[col + j]);
         ssq += x * x;
@@ -910,18 +932,19 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float4 old = reinterpret_cast<const float4*>(p)[i];
-            v[4 * i] += old.x; v[4 * i + 1] += old.y; v[4 * i + 2] += old.z; v[4 * i + 3] += old.w;
+            v[4 * i] = fmaf(ra.alpha, v[4 * i], old.x); v[4 * i + 1] = fmaf(ra.alpha, v[4 * i + 1], old.y);
+            v[4 * i + 2] = fmaf(ra.alpha, v[4 * i + 2], old.z); v[4 * i + 3] = fmaf(ra.alpha, v[4 * i + 3], old.w);
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] += gb::to_float<OT>(p[j]);
+          for (int j = 0; j < 16; ++j) v[j] = fmaf(ra.alpha, v[j], gb::to_float<OT>(p[j]));
         }
       }
       epilogue_store16<OT>(p, v, vec);
     } else {
       for (int j = 0; j < 16 && col + j < rows_n; ++j) {
         float x = v[j];
-        if (EPI == EPI_ACCUMULATE) x += gb::to_float<OT>(p[j]);
+        if (EPI == EPI_ACCUMULATE) x = fmaf(ra.alpha, x, gb::to_float<OT>(p[j]));
         store_value<OT>(p + j, x);
       }
     }
@@ -1557,9 +1580,11 @@ GB_EXPORT int gb_gemm_tc_supported(const void* x, const void* w, int Mx, int Nw,
 
 // epi 0: out[Mx,Nw] = x w^T (out_dtype f32 or bf16); 1: out (f32) += x w^T;
 // 2: w holds gate and up rows packed in groups of 64 ([128 * ceil(Nw / 64), K], see the head of this
-// file); out[Mx,Nw] (bf16) = silu(x gate^T) * (x up^T).
+// file); out[Mx,Nw] (bf16) = act(x gate^T, x up^T), act by gate_act: silu(g) u unless told otherwise.
+// alpha: the accumulating epilogue adds alpha * product. gate_act, gate_limit: the gated epilogue's
+// activation (GateAct).
 GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw, int K, int out_dtype, int epi,
-                         const GbNormFold* norm, cudaStream_t stream) {
+                         const GbNormFold* norm, float alpha, int gate_act, float gate_limit, cudaStream_t stream) {
   if (!gb_gemm_tc_supported(x, w, Mx, Nw, K))
     return gb::fail(GB_UNSUPPORTED, "gemm_tc: needs K a multiple of 8 and 16-byte aligned operands (K = %d)", K);
   if (epi == EPI_ACCUMULATE && out_dtype != GB_F32)
@@ -1570,6 +1595,10 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
   EpilogueArgs ra{};
   fold_norm(ra, norm);
   take_next_stream(ra);
+  if (gate_act < GATE_SILU || gate_act > GATE_CLAMPED_SWISH) return gb::fail(GB_BAD_ARGUMENT, "gemm_tc: gate activation %d", gate_act);
+  ra.alpha = alpha;
+  ra.gate_act = gate_act;
+  ra.gate_limit = gate_limit;
   if (ra.h_out != nullptr && epi != EPI_ACCUMULATE)
     return gb::fail(GB_UNSUPPORTED, "gemm_tc: a norm is folded in behind accumulating products only (epilogue %d)", epi);
   CUtensorMap mm, mn;

@@ -31,7 +31,7 @@ class TensorCoreKernels:
         L = self.lib
         L.gb_last_error.restype = ctypes.c_char_p
         L.gb_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                 ctypes.POINTER(NormFold), c_void_p]
+                                 ctypes.POINTER(NormFold), c_float, c_int, c_float, c_void_p]
         L.gb_gemm_tc.restype = c_int
         L.gb_gemm_tc_norm_tiles.argtypes = [c_int, c_int]
         L.gb_gemm_tc_norm_tiles.restype = c_int
@@ -115,14 +115,16 @@ class TensorCoreKernels:
             elif i >= len(self._plan) or self._plan[i][0] != w.data_ptr():
                 self._plan = None          # another step than the one that was recorded
 
-    def _gemm(self, x, w, out, n_out, epi, fold=None) -> bool:
+    def _gemm(self, x, w, out, n_out, epi, fold=None, alpha: float = 1.0, gate_act: int = 0,
+              gate_limit: float = 0.0) -> bool:
         M, K = x.shape
         if not self.lib.gb_gemm_tc_supported(x.data_ptr(), w.data_ptr(), M, n_out, K):
             return False
         self._stream(w)
         tag = 0 if out.dtype == torch.float32 else 1
         code = self.lib.gb_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, n_out, K, tag, epi,
-                                   None if fold is None else ctypes.byref(fold), self.ops._stream())
+                                   None if fold is None else ctypes.byref(fold), float(alpha), int(gate_act),
+                                   float(gate_limit), self.ops._stream())
         self.ops._check(self.lib, code, "gemm_tc")
         return True
 
@@ -130,13 +132,13 @@ class TensorCoreKernels:
         """``emit``: a ``PendingNorm`` whose values and sums this accumulating product fills."""
         if w.dtype != torch.bfloat16 or out.dtype not in (torch.float32, torch.bfloat16):
             return False
-        if alpha != 1.0:
+        if alpha != 1.0 and not accumulate:
             return False
         fold = None
         if emit is not None:
             fold = NormFold(h_out=emit.values.data_ptr(), weight=emit.weight.data_ptr(),
                             sums_out=emit.sums.data_ptr(), sums_ld=emit.sums.shape[1])
-        return self._gemm(a, w, out, w.shape[0], 1 if accumulate else 0, fold)
+        return self._gemm(a, w, out, w.shape[0], 1 if accumulate else 0, fold, alpha=alpha)
 
     def takes_qkv(self, h, w_qkv, q_out, head_dim) -> bool:
         """Whether the fused query/key/value product takes these operands (head sizes that
@@ -170,9 +172,7 @@ class TensorCoreKernels:
         if (w_gate_up.dtype != torch.bfloat16 or act.dtype != torch.bfloat16
                 or w_gate_up.shape[0] != 128 * ((F + 63) // 64)):
             return False
-        if kind != 0:
-            return False
-        return self._gemm(h, w_gate_up, act, F, 2, self._consume(pending))
+        return self._gemm(h, w_gate_up, act, F, 2, self._consume(pending), gate_act=kind, gate_limit=limit)
 
     # ------------------------------------------------------------------ attention
     def _attention_lib(self, head_dim: int):

@@ -101,6 +101,17 @@ def test_product_into_the_residual_with_a_multiplier(both, M, N, K):
     close(g, c, dt, "linear with a multiplier")
 
 
+@pytest.mark.parametrize("kind,limit", [("gelu_tanh", 0.0), ("clamped_swish", 1.0), ("silu", 0.0)])
+@pytest.mark.parametrize("M,F,K", [(1, 64, 128), (9, 320, 192), (64, 96, 64), (200, 200, 128), (700, 512, 256), (33, 50, 44)])
+def test_gate_up_product_with_the_activation_in_its_epilogue(both, kind, limit, M, F, K):
+    ops, cpu, dt = both
+    h, g, u = rnd(M, K, dtype=dt), rnd(F, K, dtype=dt, scale=0.25, seed=1), rnd(F, K, dtype=dt, scale=0.25, seed=2)
+    act, ref = torch.empty(M, F, dtype=dt, device="cuda"), torch.empty(M, F, dtype=dt)
+    ops.linear_gated(_Ctx(), h.cuda(), ops.pack_gate_up(g.cuda(), u.cuda()), act, kind, limit)
+    cpu.linear_gated(None, h, cpu.pack_gate_up(g, u), ref, kind, limit)
+    close(act, ref, dt, f"gate/up with {kind}")
+
+
 @pytest.mark.parametrize("T,E,top,K,F", [(1, 4, 4, 40, 16), (37, 16, 4, 192, 24), (130, 33, 1, 72, 50), (9, 64, 8, 256, 64)])
 def test_router_and_routed_experts(both, T, E, top, K, F):
     ops, cpu, dt = both
