@@ -139,7 +139,16 @@ def attention_lib_name(head_dim: int) -> str:
     return f"garuda_attn_hd{int(head_dim)}"
 
 
+def latent_attention_lib_name(rank: int, rot: int) -> str:
+    """The tensor-core attention over cached latent rows is compiled per (latent width, rotated
+    width), when a model first needs it."""
+    return f"garuda_latent_r{int(rank)}_t{int(rot)}"
+
+
 def _lib_recipe(name: str):
+    if name.startswith("garuda_latent_r"):
+        rank, rot = name[len("garuda_latent_r"):].split("_t")
+        return ["latent_attention_mma.cu"], [f"-DGB_LATENT_RANK={int(rank)}", f"-DGB_LATENT_ROT={int(rot)}"]
     if name.startswith("garuda_attn_hd"):
         return ["attention_mma.cu", "attention_tcgen05.cu", "attention_decode_tma.cu"], [f"-DGB_HEAD_DIM={int(name[len('garuda_attn_hd'):])}"]
     return KERNEL_LIBS[name], []
@@ -247,10 +256,12 @@ def load_host_module():
     return _HOST
 
 
-def build_all(head_dims=(16, 32, 48, 64, 128)) -> None:
+def build_all(head_dims=(16, 32, 48, 64, 128), latent_sizes=((64, 32), (512, 64))) -> None:
     """Everything, for a build check."""
     host_module_path()
     for name in KERNEL_LIBS:
         kernel_lib_path(name)
     for hd in head_dims:
         kernel_lib_path(attention_lib_name(hd))
+    for rank, rot in latent_sizes:
+        kernel_lib_path(latent_attention_lib_name(rank, rot))

@@ -440,6 +440,11 @@ class CudaOps:
               "attention: pool shape")
         _need(0 < vd <= hd, "attention: value_dim must be within the row")
         _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attention: block table")
+        if (vd < hd and Hkv == 1 and window == 0 and self.tc is not None and q.dtype == torch.bfloat16
+                and k_pool.data_ptr() == v_pool.data_ptr()
+                and self.tc.latent_attention(q, k_pool, out, block_table, cu_q, kv_lens, vd, scale, page_size,
+                                             num_requests, max_q_len, max_kv_len, ws)):
+            return          # keys and values are parts of one cached row that every head reads
         if vd == hd and self.tc is not None and q.dtype == torch.bfloat16 and self.tc.paged_attention(
                 q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, scale, window, page_size,
                 num_requests, max_q_len, max_kv_len, ws, min_q_len):

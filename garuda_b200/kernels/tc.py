@@ -11,7 +11,7 @@ from ctypes import c_void_p, c_int, c_float
 
 import torch
 
-from ..csrc.build import load_kernel_lib, attention_lib_name
+from ..csrc.build import load_kernel_lib, attention_lib_name, latent_attention_lib_name
 
 _WAIT_NAMES = {1: "an operand tile never arrived (TMA)", 2: "a pipeline stage was never released",
                3: "the accumulator never completed", 4: "copies in flight did not land while winding down",
@@ -51,6 +51,7 @@ class TensorCoreKernels:
         L.gb_tc_hint_next_stream.argtypes = [c_void_p, ctypes.c_longlong]
         L.gb_tc_hint_next_stream.restype = c_int
         self._attn = {}
+        self._latent = {}
         # The weights that the products of a step stream, in launch order: recorded during one run
         # (``record_streams``) and replayed as hints during the next (``hint_streams``), so that every
         # few-token product asks for the weights of the product behind it to be brought into L2 while
@@ -255,4 +256,57 @@ class TensorCoreKernels:
             int(k_pool.shape[0]), int(cluster), None if scratch is None else scratch.data_ptr(), need,
             self.ops._stream())
         self.ops._check(lib, code, "attention_mma", (1 if has_decode else 0) + (1 if max_q_len * g > 16 else 0))
+        return True
+
+    # ------------------------------------------------------------------ attention over cached latent rows
+    @staticmethod
+    def takes_latent(rank: int, rot: int) -> bool:
+        """Sizes the tensor-core kernel is compiled for: rows of a multiple of 16 channels, a value
+        width that splits into blocks of 16 per warp, tiles that fit the shared memory."""
+        row = rank + rot
+        return (rank >= 16 and row % 16 == 0 and rank % (32 if rank > 256 else 16) == 0 and rank <= 512
+                and 128 * (2 * row + 16) <= 227 * 1024)
+
+    def _latent_lib(self, rank: int, rot: int):
+        lib = self._latent.get((rank, rot))
+        if lib is None:
+            lib = load_kernel_lib(latent_attention_lib_name(rank, rot))
+            lib.gb_last_error.restype = ctypes.c_char_p
+            lib.gb_latent_attention.argtypes = ([c_void_p] * 4 + [c_int] + [c_void_p] * 2 + [c_int] * 3 + [c_float]
+                                                + [c_int] * 3 + [c_void_p, ctypes.c_longlong, c_void_p])
+            lib.gb_latent_attention.restype = c_int
+            lib.gb_latent_attention_scratch_bytes.argtypes = [ctypes.c_longlong, c_int]
+            lib.gb_latent_attention_scratch_bytes.restype = ctypes.c_longlong
+            self._latent[(rank, rot)] = lib
+        return lib
+
+    @staticmethod
+    def latent_plan(num_requests: int, heads: int, max_q_len: int, max_kv_len: int) -> int:
+        """CTAs that share a query tile's keys: one when the tiles alone fill the GPU, else enough for
+        about two CTAs an SM, each with at least 128 keys, at most 32."""
+        tiles = -(-max_q_len * heads // 64) * max(num_requests, 1)
+        if tiles >= 120:
+            return 1
+        return max(1, min(296 // tiles, -(-max_kv_len // 128), 32))
+
+    def latent_attention(self, q, pool, out, block_table, cu_q, kv_lens, rank, scale, page_size, num_requests,
+                         max_q_len, max_kv_len, ws=None) -> bool:
+        """``q [T, H, rank + rot]``, ``pool [pages, 1, page_size, rank + rot]``, ``out [T, H * rank]``."""
+        T, H, row = q.shape
+        rot = row - rank
+        if q.dtype != torch.bfloat16 or not self.takes_latent(rank, rot) or not scale > 0:
+            return False
+        lib = self._latent_lib(rank, rot)
+        splits = self.latent_plan(num_requests, H, max_q_len, max_kv_len)
+        while splits > 1 and lib.gb_latent_attention_scratch_bytes(T * H, splits) > (256 << 20):
+            splits //= 2
+        need = int(lib.gb_latent_attention_scratch_bytes(T * H, splits))
+        scratch = None
+        if need:
+            scratch = (ws if ws is not None else self.ops.private_ws).get("latent_partials", (need,), torch.uint8)
+        code = lib.gb_latent_attention(
+            q.data_ptr(), pool.data_ptr(), out.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+            cu_q.data_ptr(), kv_lens.data_ptr(), T, num_requests, H, float(scale), int(page_size), int(max_q_len),
+            int(splits), None if scratch is None else scratch.data_ptr(), need, self.ops._stream())
+        self.ops._check(lib, code, "latent_attention", 1 if splits == 1 else 2)
         return True

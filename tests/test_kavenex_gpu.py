@@ -181,6 +181,47 @@ def test_latent_cache_rows_head_products_and_attention_over_them(both, rank, rot
     close(o, o_c, dt, "values out of the latent")
 
 
+@pytest.mark.parametrize("rank,rot,H", [(64, 32, 4), (512, 64, 16), (96, 16, 3), (256, 32, 8)])
+@pytest.mark.parametrize("batch", ["mixed", "decode", "one long prompt"])
+def test_latent_attention_on_the_tensor_cores(rank, rot, H, batch):
+    """Unequal requests in one launch (prompt portions that start inside a page beside single
+    tokens with long and with one-token contexts), keys split over CTAs and merged, every unused
+    cache byte NaN, pages in a scrambled order."""
+    from garuda_b200.kernels.ops import CudaOps
+    from tests.plain.cpu_ops import CpuOps
+    ops, cpu, dt = CudaOps("cuda:0"), CpuOps(), torch.bfloat16
+    ps, row = 16, rank + rot
+    reqs = {"mixed": [(1, 700), (130, 130), (37, 300), (1, 1), (64, 95), (2, 33)],
+            "decode": [(1, 1500), (1, 17)], "one long prompt": [(400, 1100)]}[batch]
+    R, T = len(reqs), sum(q for q, _ in reqs)
+    width = max((kv + ps - 1) // ps for _, kv in reqs) + 1
+    pages = sum((kv + ps - 1) // ps for _, kv in reqs)
+    perm = torch.randperm(pages + 3, generator=torch.Generator().manual_seed(5)).tolist()
+    bt = torch.full((R, width), -1, dtype=torch.int32)
+    pool_c = torch.full((pages + 3, 1, ps, row), float("nan"), dtype=dt)
+    at = 0
+    for r, (_, kv) in enumerate(reqs):
+        for p in range((kv + ps - 1) // ps):
+            bt[r, p] = perm[at]
+            n = min(ps, kv - p * ps)
+            pool_c[perm[at], 0, :n] = rnd(n, row, dtype=dt, seed=at)
+            at += 1
+    q = rnd(T, H, row, dtype=dt, scale=0.6)
+    cu = torch.tensor([0] + list(np.cumsum([ql for ql, _ in reqs])), dtype=torch.int32)
+    kvl = torch.tensor([kv for _, kv in reqs], dtype=torch.int32)
+    req = torch.repeat_interleave(torch.arange(R, dtype=torch.int32), torch.tensor([ql for ql, _ in reqs]))
+    out, ref = torch.zeros(T, H * rank, dtype=dt, device="cuda"), torch.zeros(T, H * rank, dtype=dt)
+    max_q, max_kv = max(ql for ql, _ in reqs), max(kv for _, kv in reqs)
+    pool = pool_c.cuda()
+    ops.paged_attention(q.cuda(), pool, pool, bt.cuda(), cu.cuda(), kvl.cuda(), req.cuda(), out, 0.11, 0, ps, R,
+                        max_q, max_kv, value_dim=rank, min_q_len=min(ql for ql, _ in reqs))
+    assert (rank, rot) in ops.tc._latent, "the tensor-core kernel did not take these sizes"
+    if batch == "decode":
+        assert ops.tc.latent_plan(R, H, max_q, max_kv) > 1
+    cpu.paged_attention(q, pool_c, pool_c, bt, cu, kvl, req, ref, 0.11, 0, ps, R, max_q, max_kv, value_dim=rank)
+    close(out, ref, dt, f"latent attention, {batch}")
+
+
 # ---------------------------------------------------------------------------- the engine, replayed
 # bfloat16 against the 64-bit plain model, as a fraction of the largest logit: three times what a B200 showed
 TOL_BF16 = {"KA": 0.03, "KB": 0.03, "KC": 0.03, "KD": 0.03}
