@@ -35,7 +35,7 @@ KERNEL_LIBS: Dict[str, List[str]] = {
     "garuda_core": ["elementwise.cu", "gemm_simple.cu", "attention_simple.cu", "sampling.cu"],
     "garuda_tc": ["gemm_tcgen05.cu"],
     # attention over a cached latent and routed experts: built when a model first uses them
-    "garuda_mixers": ["latent.cu", "moe.cu"],
+    "garuda_mixers": ["latent.cu", "moe.cu", "moe_grouped.cu"],
 }
 HOST_SOURCES = ["cache_manager.cpp", "scheduler.cpp", "step_batch.cpp", "bindings.cpp"]
 

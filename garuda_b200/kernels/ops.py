@@ -158,6 +158,8 @@ class CudaOps:
                 fn = getattr(L, name)
                 fn.argtypes = argtypes
                 fn.restype = c_int
+            L.gb_moe_grouped_index_words.argtypes = [c_longlong, c_int]
+            L.gb_moe_grouped_index_words.restype = c_longlong
             self._mixers = L
         return self._mixers
 
@@ -172,6 +174,7 @@ class CudaOps:
                                c_int, c_float, c_void_p],
             "gb_moe_down": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                             c_float, c_void_p],
+            "gb_moe_grouped": [c_void_p] * 6 + [c_int] * 7 + [c_float, c_float] + [c_void_p] * 4,
     }
 
     def _stream(self):
@@ -586,7 +589,27 @@ class CudaOps:
         """``x[t] += alpha * sum_j weights[t, j] * expert_{ids[t, j]}(h[t])`` with the experts'
         weights stacked: ``w_gate_up [E, 2F, K]``, ``w_down [E, N, F]``."""
         T, top = ids.shape
-        act = ctx.ws.get("expert_act", (T, top, w_down.shape[2]), h.dtype)
+        E, N, F = w_down.shape
+        K = h.shape[1]
+        if self.tc is not None and h.dtype == torch.bfloat16 and K % 8 == 0 and F % 8 == 0 and E <= 4096:
+            # on the tensor cores: pairs sorted by expert on the device, two grouped products, a weighted sum
+            self._on_device(h, w_gate_up, w_down, ids, weights, x)
+            _need(h.is_contiguous() and w_gate_up.is_contiguous() and w_down.is_contiguous() and ids.is_contiguous()
+                  and weights.is_contiguous() and x.is_contiguous() and x.dtype == torch.float32
+                  and tuple(w_gate_up.shape) == (E, 2 * F, K) and x.shape == (T, N) and ids.dtype == torch.int32
+                  and weights.dtype == torch.float32 and w_gate_up.dtype == w_down.dtype == torch.bfloat16,
+                  "routed_feed_forward: shapes")
+            L = self.mixers
+            words = int(L.gb_moe_grouped_index_words(T * top, E))
+            index = ctx.ws.get("expert_index", (words,), torch.int32)
+            act = ctx.ws.get("expert_act", (T * top, F), torch.bfloat16)
+            y = ctx.ws.get("expert_rows", (T * top, N), torch.float32)
+            self._check(L, L.gb_moe_grouped(
+                h.data_ptr(), w_gate_up.data_ptr(), w_down.data_ptr(), ids.data_ptr(), weights.data_ptr(), x.data_ptr(),
+                T, top, E, F, K, N, self.GATE_ACTS[kind], float(limit), float(alpha), index.data_ptr(), act.data_ptr(),
+                y.data_ptr(), self._stream()), "moe_grouped", 4)
+            return
+        act = ctx.ws.get("expert_act", (T, top, F), h.dtype)
         self.moe_gate_up(h, w_gate_up, ids, act, kind, limit)
         self.moe_down(act, w_down, ids, weights, x, alpha)
 

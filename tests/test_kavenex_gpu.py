@@ -112,7 +112,8 @@ def test_gate_up_product_with_the_activation_in_its_epilogue(both, kind, limit, 
     close(act, ref, dt, f"gate/up with {kind}")
 
 
-@pytest.mark.parametrize("T,E,top,K,F", [(1, 4, 4, 40, 16), (37, 16, 4, 192, 24), (130, 33, 1, 72, 50), (9, 64, 8, 256, 64)])
+@pytest.mark.parametrize("T,E,top,K,F", [(1, 4, 4, 40, 16), (37, 16, 4, 192, 24), (130, 33, 1, 72, 50), (9, 64, 8, 256, 64),
+                                         (300, 5, 2, 136, 72), (700, 16, 4, 192, 64), (8, 32, 4, 512, 200)])
 def test_router_and_routed_experts(both, T, E, top, K, F):
     ops, cpu, dt = both
     h, wr, br = rnd(T, K, dtype=dt), rnd(E, K, dtype=dt, scale=0.5, seed=1), rnd(E, seed=2)
