@@ -49,6 +49,15 @@ SHAPES = {
         LLAMA, hidden_size=4096, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
         intermediate_size=14336, vocab_size=128256, rope_theta=500000.0, max_position_embeddings=8192)),
 }
+# ``--design kavenex``: the Kavenex design beside the Llama decoder at equal width, heads, head size,
+# feed-forward size and depth (random weights). Four layers each: Kavenex's are dense, routed, dense,
+# routed (a token's `top` experts together as large as the dense feed-forward, plus a shared one).
+DESIGN_SIZES = {
+    "2k": dict(width=2048, heads=32, dim=32, rot_dim=32, vdim=64, kv_rank=256, ff=5632, experts=16, top=4,
+               expert_ff=1408, shared_ff=1408, side=64, vocab=32000, llama_kv_heads=4, scale=0.125),
+    "4k": dict(width=4096, heads=32, dim=64, rot_dim=64, vdim=128, kv_rank=512, ff=11008, experts=16, top=4,
+               expert_ff=2752, shared_ff=2752, side=64, vocab=32000, llama_kv_heads=8, scale=0.088),
+}
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 NOMINAL = {"hbm_gbs": 7700.0, "bf16_tflops": 2250.0}     # HBM3e of the HGX B200; dense bfloat16 tensor rate
@@ -348,6 +357,193 @@ def run_ours(args) -> dict:
     }
 
 
+def design_configs(z):
+    mixer = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot_dim"], "vdim": z["vdim"], "kv_rank": z["kv_rank"],
+             "scale": z["scale"], "rot": {"base": 10000.0, "dims": z["rot_dim"]}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["expert_ff"], "limit": 7.0},
+           "shared": {"ff": z["shared_ff"], "limit": 7.0}}
+    kavenex = {"architecture": "Kavenex", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 1.0},
+               "norm": {"eps": 1e-5}, "residual_mult": 0.5, "token_side": {"dim": z["side"]}, "max_positions": 4096,
+               "layers": [{"type": "latent_attention", "mixer": mixer, "mlp": m} for m in (dense, moe, dense, moe)]}
+    llama = dict(LLAMA, hidden_size=z["width"], num_hidden_layers=4, num_attention_heads=z["heads"],
+                 num_key_value_heads=z["llama_kv_heads"], head_dim=z["dim"] + z["rot_dim"], intermediate_size=z["ff"],
+                 vocab_size=z["vocab"], rope_theta=10000.0, max_position_embeddings=4096)
+    return kavenex, llama
+
+
+def run_design(args) -> dict:
+    """Prefill and decode throughput of the Kavenex design and of the Llama decoder at equal sizes, and
+    the design's kernels beside the like kernels of Llama, each against its roofline (the slower of
+    bytes / measured copy rate and FLOPs / measured bfloat16 rate)."""
+    import numpy as np
+    import torch
+    from garuda_b200 import Engine, StepEntry
+    from garuda_b200.engine.batch import Workspace
+    from garuda_b200.weights import write_random_model
+
+    hbm_peak, tflops_peak, peak_kind = peaks()
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    dev = torch.device("cuda:0")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # larger than L2: written before every timed run
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        times = []
+        for _ in range(reps):
+            flush.zero_()
+            s, e = ev(), ev()
+            torch.cuda.synchronize()
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            times.append(s.elapsed_time(e))
+        return sorted(times)[len(times) // 2]
+
+    def roof(ms, flops=0.0, nbytes=0.0):
+        ideal = max(flops / (tflops_peak * 1e12), nbytes / (hbm_peak * 1e9)) * 1e3
+        return {"ms": round(ms, 4), "roofline_ms": round(ideal, 4), "frac": round(ideal / ms, 4)}
+
+    out = {"design": "kavenex", "peaks": peak_kind, "hbm_gbs": hbm_peak, "bf16_tflops": tflops_peak, "dtype": "bf16",
+           "data": "synthetic", "timing": "CUDA events, 3 warm-up runs, L2 flushed before every timed run, median", "sizes": {}}
+    B, CTX, T = 8, 2048, PREFILL_TOKENS
+    for name in (args.size.split(",") if args.size else list(DESIGN_SIZES)):
+        z = DESIGN_SIZES[name]
+        rec = {}
+        engines = {}
+        for arch, cfg in zip(("kavenex", "llama"), design_configs(z)):
+            tmp = tempfile.mkdtemp(prefix="garuda_bench_", dir="/dev/shm" if os.path.isdir("/dev/shm") else None)
+            try:
+                write_random_model(tmp, cfg, seed=0, store_dtype=torch.bfloat16)
+                engine = Engine(tmp, dtype="bfloat16", context=4096, page_size=32, kv_tokens=B * CTX + 4096 + 64,
+                                max_concurrent=B, max_batch_tokens=T, prefill_chunk=T, ignore_eos=True)
+            finally:
+                shutil.rmtree(tmp, ignore_errors=True)
+            engines[arch] = engine
+            runner, rng, V = engine.runner, np.random.default_rng(0), z["vocab"]
+            toks = rng.integers(0, V, T).tolist()
+            rid = [0]
+
+            def prefill():
+                rid[0] += 1
+                runner.run([StepEntry(10_000 + rid[0], toks, [T - 1])])
+                runner.end(10_000 + rid[0])
+
+            ms = timed(prefill, reps=5)
+            rec[arch] = {"prefill_2048_ms": round(ms, 3), "prefill_tok_s": round(T / ms * 1e3)}
+            steps = 48
+            for r in range(B):
+                runner.run([StepEntry(r, rng.integers(0, V, CTX - steps - 8).tolist(), [])])
+            feed = rng.integers(0, V, (steps + 8, B))
+            for i in range(8):
+                runner.run([StepEntry(r, [int(feed[i, r])], [0]) for r in range(B)])
+            marks = [ev() for _ in range(steps + 1)]
+            torch.cuda.synchronize()
+            marks[0].record()
+            for i in range(steps):
+                runner.run([StepEntry(r, [int(feed[8 + i, r])], [0]) for r in range(B)])
+                marks[i + 1].record()
+            torch.cuda.synchronize()
+            each = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(steps))
+            for r in range(B):
+                runner.end(r)
+            rec[arch].update({"decode_b8_ctx2048_ms": round(each[len(each) // 2], 4),
+                              "decode_tok_s": round(B / each[len(each) // 2] * 1e3),
+                              "graph_replays": runner.graphs.replays})
+            if engine.ops.tc is not None:
+                engine.ops.tc.check_errors()
+        # ------------------------------------------------------------ kernel beside like kernel
+        ops = engines["kavenex"].ops
+        bf = torch.bfloat16
+        H, rank, rot, dn, dv, W = z["heads"], z["kv_rank"], z["rot_dim"], z["dim"], z["vdim"], z["width"]
+        row, hd, Hkv, ps = rank + rot, z["dim"] + z["rot_dim"], z["llama_kv_heads"], 32
+        ws = Workspace(dev)
+
+        class Ctx:
+            pass
+        ctx = Ctx()
+        ctx.ws = ws
+        ctx.step_cache = {}
+        kern = {}
+
+        def paged(nreq, q_len, kv_len, heads, width, pools):
+            pages = (kv_len + ps - 1) // ps
+            bt = torch.arange(nreq * pages, dtype=torch.int32, device=dev).view(nreq, pages)
+            cu = torch.arange(nreq + 1, dtype=torch.int32, device=dev) * q_len
+            kvl = torch.full((nreq,), kv_len, dtype=torch.int32, device=dev)
+            req = torch.arange(nreq, dtype=torch.int32, device=dev).repeat_interleave(q_len)
+            q = torch.randn(nreq * q_len, heads, width, device=dev).to(bf)
+            pool = [torch.randn(nreq * pages, kvh, ps, w_, device=dev).to(bf) for kvh, w_ in pools]
+            return q, pool, bt, cu, kvl, req
+
+        for label, nreq, q_len, kv_len in (("prefill_2048", 1, T, T), ("decode_b8_ctx2048", B, 1, CTX)):
+            keys = nreq * (q_len * (kv_len - q_len) + q_len * (q_len + 1) // 2)
+            q, (pool,), bt, cu, kvl, req = paged(nreq, q_len, kv_len, H, row, [(1, row)])
+            o = torch.empty(nreq * q_len, H * rank, dtype=bf, device=dev)
+            ms = timed(lambda: ops.paged_attention(q, pool, pool, bt, cu, kvl, req, o, 0.1, 0, ps, nreq, q_len, kv_len,
+                                                   ws=ws, min_q_len=q_len, value_dim=rank))
+            kern[f"latent_attention_{label}"] = roof(ms, 2.0 * H * (row + rank) * keys,
+                                                     2.0 * (nreq * kv_len * row + q.numel() + o.numel()))
+            q, (kp, vp), bt, cu, kvl, req = paged(nreq, q_len, kv_len, H, hd, [(Hkv, hd), (Hkv, hd)])
+            o = torch.empty(nreq * q_len, H * hd, dtype=bf, device=dev)
+            ms = timed(lambda: ops.paged_attention(q, kp, vp, bt, cu, kvl, req, o, 0.1, 0, ps, nreq, q_len, kv_len, ws=ws,
+                                                   min_q_len=q_len))
+            kern[f"llama_attention_{label}"] = roof(ms, 4.0 * H * hd * keys,
+                                                    2.0 * (2 * nreq * kv_len * Hkv * hd + q.numel() + o.numel()))
+        for label, M in (("2048_tokens", T), ("8_tokens", B)):
+            h = torch.randn(M, W, device=dev).to(bf)
+            x = torch.zeros(M, W, device=dev)
+            E, top, F = z["experts"], z["top"], z["expert_ff"]
+            wgu = (torch.randn(E, 2 * F, W, device=dev) * 0.02).to(bf)
+            wd = (torch.randn(E, W, F, device=dev) * 0.02).to(bf)
+            wr = (torch.randn(E, W, device=dev) * 0.5).to(bf)
+            ids = torch.empty(M, top, dtype=torch.int32, device=dev)
+            wt = torch.empty(M, top, device=dev)
+
+            def routed():
+                ops.route_topk(h, wr, None, top, ids, wt)
+                ops.routed_feed_forward(ctx, h, wgu, wd, ids, wt, x, "clamped_swish", 7.0, 0.5)
+
+            ms = timed(routed)
+            used = min(E, M * top)
+            kern[f"routed_experts_{label}"] = roof(ms, 2.0 * M * top * 3 * F * W, 2.0 * used * 3 * F * W)
+            FF = z["ff"]
+            g = ops.pack_gate_up((torch.randn(FF, W, device=dev) * 0.02).to(bf), (torch.randn(FF, W, device=dev) * 0.02).to(bf))
+            dwn = (torch.randn(W, FF, device=dev) * 0.02).to(bf)
+            act = torch.empty(M, FF, dtype=bf, device=dev)
+
+            def dense(kind):
+                ops.linear_gated(ctx, h, g, act, kind, 0.0)
+                ops.linear(act, dwn, x, accumulate=True, alpha=0.5)
+
+            kern[f"dense_gelu_feed_forward_{label}"] = roof(timed(lambda: dense("gelu_tanh")), 2.0 * M * 3 * FF * W, 2.0 * 3 * FF * W)
+            kern[f"llama_silu_feed_forward_{label}"] = roof(timed(lambda: dense("silu")), 2.0 * M * 3 * FF * W, 2.0 * 3 * FF * W)
+            del wgu, wd, g, dwn
+        qn = torch.randn(T, H, dn, device=dev).to(bf)
+        wuk = (torch.randn(H * rank, dn, device=dev) * 0.05).to(bf)
+        ql = torch.empty(T, H, row, dtype=bf, device=dev)
+        kern["query_into_latent_2048_tokens"] = roof(timed(lambda: ops.head_linear(qn, wuk, ql, rank, dn, False)),
+                                                     2.0 * T * H * dn * rank, 2.0 * (qn.numel() + T * H * rank))
+        mixed = torch.randn(T, H, rank, device=dev).to(bf)
+        wuv = (torch.randn(H * dv, rank, device=dev) * 0.05).to(bf)
+        oo = torch.empty(T, H, dv, dtype=bf, device=dev)
+        kern["values_out_of_latent_2048_tokens"] = roof(timed(lambda: ops.head_linear(mixed, wuv, oo, dv, rank, False)),
+                                                        2.0 * T * H * dv * rank, 2.0 * (mixed.numel() + oo.numel()))
+        xr = torch.randn(T, W, device=dev)
+        wv, bv = torch.ones(W, dtype=bf, device=dev), torch.zeros(W, dtype=bf, device=dev)
+        on = torch.empty(T, W, dtype=bf, device=dev)
+        kern["layer_norm_2048_tokens"] = roof(timed(lambda: ops.layernorm(xr, wv, bv, 1e-5, on)), 0, 6.0 * T * W)
+        kern["llama_rms_norm_2048_tokens"] = roof(timed(lambda: ops.rmsnorm(xr, wv, 1e-5, on)), 0, 6.0 * T * W)
+        rec["kernels"] = kern
+        rec["config"] = {k: v for k, v in z.items()}
+        out["sizes"][name] = rec
+        del engines
+        torch.cuda.empty_cache()
+    return out
+
+
 def cpu_reference_seconds() -> dict:
     """The reference is a CPU engine; it cannot be built here, so the nearest thing to its time is
     the plain implementation of the tests (its formulas, numpy, 32-bit, no cache) on the smallest of
@@ -460,6 +656,9 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=0, help="context reached with --only decode (default: the shape's); keys with --only attention")
     ap.add_argument("--layers", type=int, default=0,
                     help="fewer layers than the configuration has (reported beside the full number)")
+    ap.add_argument("--design", choices=["kavenex"],
+                    help="instead of the default workload: this design beside the Llama decoder at equal sizes")
+    ap.add_argument("--size", default="", help="with --design: which of its sizes (2k, 4k; default both)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -474,6 +673,9 @@ def main() -> int:
     if not 1 <= args.batch <= 64:
         print("bench.py: --batch must be 1 to 64")
         return 2
+    if args.design:
+        print(json.dumps(run_design(args)))
+        return 0
     print(json.dumps(run_ours(args)))
     return 0
 

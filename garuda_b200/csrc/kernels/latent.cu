@@ -59,6 +59,42 @@ latent_append_kernel(const float* __restrict__ src, int row_stride, const WT* __
   for (int c = rot_dims + threadIdx.x; c < rot; c += blockDim.x) dst[rank + c] = gb::from_float<OT>(r[c]);
 }
 
+// One block per token. src row: H heads of [unrotated (dn) | rotated part (rot)] in 32-bit. The
+// unrotated parts go to q_nope [T, H, dn]; the rotated parts, turned like the keys' (pairs
+// (2i, 2i + 1) of the first rot_dims channels by pos * inv_freq[i]), go to the last `rot` channels of
+// q_lat's rows [T, H, lat_row], whose first channels a product fills afterwards.
+template <typename OT>
+__global__ void __launch_bounds__(256)
+latent_query_prepare_kernel(const float* __restrict__ src, int row_stride, int H, int dn, int rot, int rot_dims,
+                            const float* __restrict__ inv_freq, const int32_t* __restrict__ positions,
+                            OT* __restrict__ q_nope, OT* __restrict__ q_lat, int lat_row) {
+  gb::pdl_launch_dependents();
+  gb::pdl_wait();
+  const int t = blockIdx.x;
+  const float* s = src + (size_t)t * row_stride;
+  const int pos = positions[t];
+  const int hw = dn + rot;
+  for (int e = threadIdx.x; e < H * dn; e += blockDim.x) {
+    const int h = e / dn, c = e % dn;
+    q_nope[(size_t)t * H * dn + e] = gb::from_float<OT>(s[h * hw + c]);
+  }
+  const int half = rot_dims / 2;
+  for (int e = threadIdx.x; e < H * half; e += blockDim.x) {
+    const int h = e / half, i = e % half;
+    float sn, cs;
+    sincosf((float)pos * inv_freq[i], &sn, &cs);
+    const float a = s[h * hw + dn + 2 * i], b = s[h * hw + dn + 2 * i + 1];
+    OT* dst = q_lat + ((size_t)t * H + h) * lat_row + (lat_row - rot);
+    dst[2 * i] = gb::from_float<OT>(a * cs - b * sn);
+    dst[2 * i + 1] = gb::from_float<OT>(b * cs + a * sn);
+  }
+  const int rest = rot - rot_dims;
+  for (int e = threadIdx.x; e < H * rest; e += blockDim.x) {
+    const int h = e / rest, c = rot_dims + e % rest;
+    q_lat[((size_t)t * H + h) * lat_row + (lat_row - rot) + c] = gb::from_float<OT>(s[h * hw + dn + c]);
+  }
+}
+
 // out[t][h][n] = sum_k a[t][h][k] * w_h[n][k], n < N, and out[t][h][N + j] = a[t][h][K + j], j < tail.
 // w_h[n][k] lies at w[h * w_head + n * w_n + k * w_k]: either w_n == 1 (consecutive n are adjacent:
 // a thread per n) or w_k == 1 (a warp per n, lanes over k). TOK tokens share one pass over the
@@ -134,6 +170,21 @@ GB_EXPORT int gb_latent_append(const float* src, int row_stride, const void* nor
                          table_width, page_size, (OT*)pool),
           "latent_append");
     });
+  });
+}
+
+GB_EXPORT int gb_latent_query_prepare(const float* src, int row_stride, int H, int dn, int rot, int rot_dims,
+                                      const float* inv_freq, const int32_t* positions, void* q_nope, void* q_lat,
+                                      int out_dtype, int lat_row, int T, cudaStream_t stream) {
+  if (T <= 0) return GB_OK;
+  if (H < 1 || dn < 1 || rot < 0 || rot_dims < 0 || rot_dims > rot || rot_dims % 2 || lat_row < rot)
+    return gb::fail(GB_BAD_ARGUMENT, "latent_query_prepare: heads %d, %d + %d channels of which %d turned", H, dn, rot, rot_dims);
+  if (rot_dims > 0 && !inv_freq) return gb::fail(GB_BAD_ARGUMENT, "latent_query_prepare: a rotation without frequencies");
+  return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
+    return gb::check_pdl_launch(
+        gb::launch_pdl(latent_query_prepare_kernel<OT>, dim3(T), dim3(256), 0, stream, dim3(1, 1, 1), src, row_stride, H, dn,
+                       rot, rot_dims, inv_freq, positions, (OT*)q_nope, (OT*)q_lat, lat_row),
+        "latent_query_prepare");
   });
 }
 

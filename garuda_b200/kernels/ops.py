@@ -175,6 +175,10 @@ class CudaOps:
             "gb_moe_down": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                             c_float, c_void_p],
             "gb_moe_grouped": [c_void_p] * 6 + [c_int] * 7 + [c_float, c_float] + [c_void_p] * 4,
+            "gb_grouped_gemm": [c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_longlong,
+                                c_int, c_int, c_int, c_int, c_void_p],
+            "gb_latent_query_prepare": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_int, c_int, c_int, c_void_p],
     }
 
     def _stream(self):
@@ -633,6 +637,25 @@ class CudaOps:
             block_table.shape[1], int(page_size), pool.data_ptr(), _tag(pool, "latent pool"), T, self._stream()),
             "latent_append")
 
+    def latent_query_prepare(self, src, heads, dn, rot, rotary, positions, q_nope, q_lat):
+        """From a step's 32-bit query rows ``src [T, heads * (dn + rot)]`` (a view with any row
+        stride): the unrotated parts to ``q_nope [T, heads, dn]``, the rotated parts, turned at the
+        tokens' positions, to the last ``rot`` channels of ``q_lat [T, heads, *]``."""
+        self._on_device(src, positions, q_nope, q_lat)
+        T = src.shape[0]
+        _need(src.dtype == torch.float32 and src.stride(1) == 1 and src.shape[1] == heads * (dn + rot), "latent_query_prepare: src")
+        _need(q_nope.is_contiguous() and q_lat.is_contiguous() and q_nope.dtype == q_lat.dtype
+              and tuple(q_nope.shape) == (T, heads, dn) and q_lat.shape[:2] == (T, heads) and q_lat.shape[2] >= rot,
+              "latent_query_prepare: outputs")
+        inv, dims = None, 0
+        if rotary is not None:
+            _need(rotary.interleaved and rotary.head_dim <= rot, "latent_query_prepare: pairs (2i, 2i + 1) within the rotated part")
+            inv, dims = self.inv_freq(rotary), rotary.head_dim
+        self._check(self.mixers, self.mixers.gb_latent_query_prepare(
+            src.data_ptr(), src.stride(0), int(heads), int(dn), int(rot), int(dims), _ptr(inv), positions.data_ptr(),
+            q_nope.data_ptr(), q_lat.data_ptr(), _tag(q_lat, "q_lat"), q_lat.shape[2], T, self._stream()),
+            "latent_query_prepare")
+
     def head_linear(self, a, w, out, n, k, transposed: bool, tail: int = 0):
         """One small product per head: ``out[t, h, :n] = a[t, h, :k] @ w_h^T`` and
         ``out[t, h, n:n + tail] = a[t, h, k:k + tail]``. ``a [T, H, >= k + tail]`` and ``out
@@ -644,6 +667,13 @@ class CudaOps:
         _need(a.dim() == 3 and out.dim() == 3 and a.stride(2) == 1 and out.stride(2) == 1 and out.shape[:2] == (T, H)
               and a.shape[2] >= k + tail and out.shape[2] >= n + tail, "head_linear: a and out are [T, H, *] views")
         _need(w.is_contiguous() and tuple(w.shape) == ((H * k, n) if transposed else (H * n, k)), "head_linear: weight shape")
+        if (self.tc is not None and not transposed and tail == 0 and a.dtype == w.dtype == out.dtype == torch.bfloat16
+                and k % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) % 8 == 0 and a.data_ptr() % 16 == 0):
+            # on the tensor cores: one grouped product, a group per head
+            self._check(self.mixers, self.mixers.gb_grouped_gemm(
+                a.data_ptr(), a.stride(0), a.stride(1), w.data_ptr(), n * k, out.data_ptr(), out.stride(0),
+                out.stride(1), H, T, int(n), int(k), self._stream()), "grouped_gemm")
+            return
         w_n, w_k = (1, n) if transposed else (k, 1)
         self._check(self.mixers, self.mixers.gb_head_gemm(
             a.data_ptr(), _tag(a, "a"), a.stride(0), a.stride(1), w.data_ptr(), _tag(w, "w"), n * k, w_n, w_k,

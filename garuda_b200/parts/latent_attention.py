@@ -81,7 +81,10 @@ class LatentAttention(Mixer):
         # the query and the down projection are one product against their rows stacked
         self.w_qd = torch.cat([tensors[q], tensors[dkv]], dim=0).contiguous()
         self.norm_w = tensors[norm]
-        self.w_uk = tensors[uk].contiguous()
+        # W_uk per head, transposed once: [H * rank, dim], so that the query's map into the latent's
+        # coordinates is a product against rows like every other
+        self.w_uk_t = (tensors[uk].view(self.heads, self.dim, self.rank).transpose(1, 2).contiguous()
+                       .view(self.heads * self.rank, self.dim))
         self.w_uv = tensors[uv].contiguous()
         self.w_o = tensors[o].contiguous()
 
@@ -90,15 +93,14 @@ class LatentAttention(Mixer):
         T, H = h.shape[0], self.heads
         qd = ws.get("latent_qd", (T, self.q_width + self.row), torch.float32)
         ops.linear(h, self.w_qd, qd)
-        qv = qd[:, :self.q_width].unflatten(1, (H, self.dim + self.rot_dim))
-        if self.rotary is not None:
-            ops.rope_inplace(qv[..., self.dim:self.dim + self.rot_dims], b.positions, self.rotary)
         if cache.writes:
             ops.latent_append(qd[:, self.q_width:], self.norm_w, self.eps, self.rank, self.rot_dim, self.rotary,
                               b.positions, b.token_req, cache.block_table, cache.k, cache.page_size)
         # the query in the latent's coordinates: [W_uk^T q^n | q^r]
         q_lat = ws.get("latent_q", (T, H, self.row), self.dtype)
-        ops.head_linear(qv, self.w_uk, q_lat, n=self.rank, k=self.dim, transposed=True, tail=self.rot_dim)
+        q_nope = ws.get("latent_q_nope", (T, H, self.dim), self.dtype)
+        ops.latent_query_prepare(qd[:, :self.q_width], H, self.dim, self.rot_dim, self.rotary, b.positions, q_nope, q_lat)
+        ops.head_linear(q_nope, self.w_uk_t, q_lat, n=self.rank, k=self.dim, transposed=False)
         mixed = ws.get("latent_ctx", (T, H * self.rank), self.dtype)
         ops.paged_attention(q_lat, cache.k, cache.k, cache.block_table, b.cu_q, b.kv_lens, b.token_req, mixed,
                             self.scale, self.window or 0, cache.page_size, b.num_requests, b.max_q_len,

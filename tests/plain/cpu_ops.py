@@ -235,6 +235,17 @@ class CpuOps:
             if page >= 0:
                 pool[page, 0, pos % page_size, :] = row[t].to(pool.dtype)
 
+    def latent_query_prepare(self, src, heads, dn, rot, rotary, positions, q_nope, q_lat):
+        """unrotated query parts to q_nope, rotated parts (turned) to the last rot channels of q_lat"""
+        T = src.shape[0]
+        v = src.reshape(T, heads, dn + rot)
+        q_nope.copy_(v[..., :dn].to(q_nope.dtype))
+        r = v[..., dn:].clone()
+        if rotary is not None:
+            d = rotary.head_dim
+            r[..., :d] = self._rotate(r[..., :d], positions, rotary)
+        q_lat[..., q_lat.shape[2] - rot:] = r.to(q_lat.dtype)
+
     def head_linear(self, a, w, out, n, k, transposed, tail=0):
         T, H = a.shape[:2]
         wf = w.float()

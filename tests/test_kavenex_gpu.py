@@ -182,6 +182,25 @@ def test_latent_cache_rows_head_products_and_attention_over_them(both, rank, rot
     close(o, o_c, dt, "values out of the latent")
 
 
+@pytest.mark.parametrize("T,H,dn,rot,dims,rank", [(5, 3, 10, 8, 6, 24), (300, 4, 32, 32, 32, 96), (70, 16, 64, 64, 64, 512)])
+def test_query_rows_prepared_and_mapped_into_the_latent(both, T, H, dn, rot, dims, rank):
+    from garuda_b200.parts.rotary import RotaryParams
+    ops, cpu, dt = both
+    rp = RotaryParams(1e4, dims, True, tuple(float(1e4 ** (-2 * i / dims)) for i in range(dims // 2)))
+    src = rnd(T, H * (dn + rot) + 9)[:, :H * (dn + rot)]
+    pos = torch.arange(7, 7 + T, dtype=torch.int32)
+    qn, ql = torch.zeros(T, H, dn, dtype=dt, device="cuda"), torch.zeros(T, H, rank + rot, dtype=dt, device="cuda")
+    qn_c, ql_c = torch.zeros(T, H, dn, dtype=dt), torch.zeros(T, H, rank + rot, dtype=dt)
+    ops.latent_query_prepare(src.cuda(), H, dn, rot, rp, pos.cuda(), qn, ql)
+    cpu.latent_query_prepare(src, H, dn, rot, rp, pos, qn_c, ql_c)
+    close(qn, qn_c, dt, "unrotated query parts")
+    close(ql, ql_c, dt, "rotated query parts")
+    w = rnd(H * rank, dn, dtype=dt, scale=0.3, seed=1)
+    ops.head_linear(qn_c.cuda(), w.cuda(), ql, rank, dn, False)
+    cpu.head_linear(qn_c, w, ql_c, rank, dn, False)
+    close(ql, ql_c, dt, "query in the latent's coordinates")
+
+
 @pytest.mark.parametrize("rank,rot,H", [(64, 32, 4), (512, 64, 16), (96, 16, 3), (256, 32, 8)])
 @pytest.mark.parametrize("batch", ["mixed", "decode", "one long prompt"])
 def test_latent_attention_on_the_tensor_cores(rank, rot, H, batch):
