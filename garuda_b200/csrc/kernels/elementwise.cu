@@ -289,6 +289,48 @@ layernorm_kernel(const float* __restrict__ x, const WT* __restrict__ w, const WT
   }
 }
 
+// Rows of up to 4096 values whose length is a multiple of 4: the row is read once, 16 bytes per
+// load, and stays in registers between the mean, the variance and the scaling.
+template <typename WT, typename OT>
+__global__ void __launch_bounds__(256)
+layernorm_vec_kernel(const float* __restrict__ x, const WT* __restrict__ w, const WT* __restrict__ b, float eps,
+                     OT* __restrict__ out, const int32_t* __restrict__ rows, int d) {
+  gb::pdl_launch_dependents();
+  gb::pdl_wait();
+  __shared__ float part[32];
+  const int r = blockIdx.x;
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * d);
+  const int nvec = d >> 2;
+  float4 v[4];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = threadIdx.x + i * 256;
+    v[i] = c < nvec ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+  }
+  const float mean = block_sum(s, part) / (float)d;
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (threadIdx.x + i * 256 >= nvec) continue;
+    const float a0 = v[i].x - mean, a1 = v[i].y - mean, a2 = v[i].z - mean, a3 = v[i].w - mean;
+    ss = fmaf(a0, a0, ss); ss = fmaf(a1, a1, ss); ss = fmaf(a2, a2, ss); ss = fmaf(a3, a3, ss);
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, part) / (float)d + eps);
+  OT* o = out + (size_t)r * d;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = threadIdx.x + i * 256;
+    if (c >= nvec) continue;
+    float y[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      y[j] = ((y[j] - mean) * inv) * gb::to_float<WT>(w[4 * c + j]) + (b ? gb::to_float<WT>(b[4 * c + j]) : 0.f);
+    store4<OT>(o + 4 * c, y[0], y[1], y[2], y[3]);
+  }
+}
+
 // x[t][c] += alpha * y[t][c] + row[c]; y or row may be absent
 template <typename YT, typename RT>
 __global__ void residual_axpy_kernel(float* __restrict__ x, const YT* __restrict__ y, float alpha,
@@ -309,10 +351,24 @@ rms_add_kernel(float* __restrict__ x, const float* __restrict__ y, const WT* __r
   __shared__ float part[32];
   const float* yr = y + (size_t)blockIdx.x * d;
   float* xr = x + (size_t)blockIdx.x * d;
+  // up to 16 values a thread stay in registers between the sum and the scaling (rows of up to 4096
+  // with 256 threads); a longer row's other values are read again
+  float keep[16];
   float ss = 0.f;
-  for (int c = threadIdx.x; c < d; c += blockDim.x) ss = fmaf(yr[c], yr[c], ss);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    keep[i] = c < d ? yr[c] : 0.f;
+    ss = fmaf(keep[i], keep[i], ss);
+  }
+  for (int c = threadIdx.x + 16 * blockDim.x; c < d; c += blockDim.x) ss = fmaf(yr[c], yr[c], ss);
   const float inv = 1.0f / sqrtf(block_sum(ss, part) / (float)d + eps);
-  for (int c = threadIdx.x; c < d; c += blockDim.x)
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < d) xr[c] = fmaf(alpha, (keep[i] * inv) * gb::to_float<WT>(w[c]), xr[c]);
+  }
+  for (int c = threadIdx.x + 16 * blockDim.x; c < d; c += blockDim.x)
     xr[c] = fmaf(alpha, (yr[c] * inv) * gb::to_float<WT>(w[c]), xr[c]);
 }
 
@@ -463,6 +519,10 @@ GB_EXPORT int gb_layernorm(const float* x, const void* w, const void* b, int w_d
   if (n_rows <= 0) return GB_OK;
   return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
     return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
+      if (d % 4 == 0 && d <= 4096 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0)
+        return gb::check_pdl_launch(gb::launch_pdl(layernorm_vec_kernel<WT, OT>, dim3(n_rows), dim3(256), 0, stream,
+                                                   dim3(1, 1, 1), x, (const WT*)w, (const WT*)b, eps, (OT*)out, rows, d),
+                                    "layernorm");
       return gb::check_pdl_launch(gb::launch_pdl(layernorm_kernel<WT, OT>, dim3(n_rows), dim3(d >= 1024 ? 256 : 128), 0,
                                                  stream, dim3(1, 1, 1), x, (const WT*)w, (const WT*)b, eps, (OT*)out,
                                                  rows, d), "layernorm");
@@ -486,7 +546,7 @@ GB_EXPORT int gb_rms_add(float* x, const float* y, const void* w, int w_dtype, f
                          cudaStream_t stream) {
   if (T <= 0) return GB_OK;
   return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
-    rms_add_kernel<WT><<<T, d >= 1024 ? 256 : 128, 0, stream>>>(x, y, (const WT*)w, eps, alpha, d);
+    rms_add_kernel<WT><<<T, 256, 0, stream>>>(x, y, (const WT*)w, eps, alpha, d);
     return gb::check_launch("rms_add");
   });
 }

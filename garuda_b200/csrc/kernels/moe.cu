@@ -11,28 +11,32 @@ namespace {
 constexpr int MAX_EXPERTS = 512;
 constexpr int MAX_TOP = 32;
 
-// One warp per token. z_e = h . W[e] + b[e] in 32-bit (the bias is 32-bit); the chosen experts in descending order of
-// their logit (the lower index first among equals); weights = softmax over the chosen logits.
+// One block per token: its warps share out the experts (z_e = h . W[e] + b[e] in 32-bit, the bias
+// 32-bit, each logit one warp's sum in a fixed order), then warp 0 picks the `top` largest in
+// descending order (the lower index first among equals); weights = softmax over the chosen logits.
 template <typename HT, typename WT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 route_topk_kernel(const HT* __restrict__ h, const WT* __restrict__ w, const float* __restrict__ bias, int T, int E,
                   int K, int top, int32_t* __restrict__ ids, float* __restrict__ weights) {
   gb::pdl_launch_dependents();
   gb::pdl_wait();
-  extern __shared__ float z_s[];       // [4][E]
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 4 + warp;
-  if (t >= T) return;
-  float* z = z_s + warp * E;
+  extern __shared__ float sm[];        // z[E], then h[K]
+  float* z = sm;
+  float* h_s = sm + E;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const int t = blockIdx.x;
   const HT* hr = h + (size_t)t * K;
-  for (int e = 0; e < E; ++e) {
+  for (int k = threadIdx.x; k < K; k += blockDim.x) h_s[k] = gb::to_float<HT>(hr[k]);
+  __syncthreads();
+  for (int e = warp; e < E; e += warps) {
     const WT* wr = w + (size_t)e * K;
     float acc = 0.f;
-    for (int k = lane; k < K; k += 32) acc = fmaf(gb::to_float<HT>(hr[k]), gb::to_float<WT>(wr[k]), acc);
+    for (int k = lane; k < K; k += 32) acc = fmaf(h_s[k], gb::to_float<WT>(wr[k]), acc);
     acc = gb::warp_sum(acc);
     if (lane == 0) z[e] = acc + (bias ? bias[e] : 0.f);
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   // `top` rounds of a warp-wide arg-max; a chosen expert's logit is replaced by -inf
   float chosen[MAX_TOP];
   for (int j = 0; j < top; ++j) {
@@ -130,10 +134,16 @@ GB_EXPORT int gb_route_topk(const void* h, int h_dtype, const void* w, const flo
   if (T <= 0) return GB_OK;
   if (E < 1 || E > MAX_EXPERTS || top < 1 || top > MAX_TOP || top > E)
     return gb::fail(GB_UNSUPPORTED, "route_topk: %d of %d experts (at most %d of %d)", top, E, MAX_TOP, MAX_EXPERTS);
+  const size_t smem = (size_t)(E + K) * sizeof(float);
+  if (smem > 200 * 1024) return gb::fail(GB_UNSUPPORTED, "route_topk: width %d", K);
   return GB_DISPATCH_DTYPE(h_dtype, HT, [&]() -> int {
     return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
+      if (smem > 48 * 1024) {     // rare (rows beyond 12,000 values): asked for at every such launch
+        cudaError_t e = cudaFuncSetAttribute(route_topk_kernel<HT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "route_topk: %s", cudaGetErrorString(e));
+      }
       return gb::check_pdl_launch(
-          gb::launch_pdl(route_topk_kernel<HT, WT>, dim3((T + 3) / 4), dim3(128), (size_t)4 * E * sizeof(float), stream,
+          gb::launch_pdl(route_topk_kernel<HT, WT>, dim3(T), dim3(256), smem, stream,
                          dim3(1, 1, 1), (const HT*)h, (const WT*)w, bias, T, E, K, top, ids, weights),
           "route_topk");
     });

@@ -85,7 +85,10 @@ def main(argv=None) -> int:
     from .engine import Engine
 
     load_plugins(args.plugin)
-    engine = Engine(args.model, dtype=args.dtype, page_size=args.page_size, kv_tokens=args.max_tokens,
+    # no request can hold more than the pool does: block tables need be no wider than that (a model
+    # with a shorter limit of its own keeps it)
+    pool = max((args.max_tokens + args.page_size - 1) // args.page_size * args.page_size, 2 * args.page_size)
+    engine = Engine(args.model, dtype=args.dtype, page_size=args.page_size, kv_tokens=args.max_tokens, context=pool,
                     max_concurrent=args.max_requests, cuda_graphs=not args.no_graphs)
     replay(engine, sys.stdin, args.out, report=_say_done)
     return 0

@@ -46,7 +46,7 @@ def close(got, want, dt, what):
     assert torch.isfinite(got).all() and err <= tol, f"{what}: {err:.2e}"
 
 
-@pytest.mark.parametrize("T,d", [(1, 40), (37, 192), (5, 1030)])
+@pytest.mark.parametrize("T,d", [(1, 40), (37, 192), (5, 1030), (3, 4096), (2, 6000), (4, 2052)])
 def test_layer_norm_rms_add_and_residual_forms(both, T, d):
     ops, cpu, dt = both
     x, y, w, b = rnd(T, d), rnd(T, d, seed=1), rnd(d, dtype=dt, seed=2), rnd(d, dtype=dt, seed=3)
