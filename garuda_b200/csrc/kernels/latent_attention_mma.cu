@@ -11,9 +11,11 @@
 // is the point of keeping one row per position (the cache is read once per tile, not per head).
 //
 // A CTA: 64 query rows (four row blocks of 16), tiles of 32 keys through a two-stage cp.async
-// ring. A warp owns one row block and VCOLS of the value columns; with RANK > 256 two warps share
-// a row block (each computes the block's scores, which costs arithmetic but no exchange, and
-// half of the values). Keys may be split over CTAs (grid.z): every CTA then writes unnormalised
+// ring. A warp owns one row block and VCOLS of the value columns; with RANK > 256 (an accumulator
+// too large for one warp's registers) two warps share a row block: each computes the scores of 16
+// of a tile's 32 keys and half of the value columns, and they exchange the rows' maxima and the
+// probabilities (as packed A fragments, which are laid out alike in both warps) through shared
+// memory, meeting at a barrier of their own. Keys may be split over CTAs (grid.z): every CTA then writes unnormalised
 // sums with its running maximum and denominator, and a second kernel merges them in split order.
 // A masked key's row is zero-filled in shared memory, so that whatever lies in pages not yet
 // written (NaN included) never reaches a sum.
@@ -112,6 +114,11 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const int qpos0 = i0 < rows ? start_pos + i0 / H : -1;
   const int qpos1 = i1 < rows ? start_pos + i1 / H : -1;
   const bool active = rb * 16 < rows_here;
+  // what the two warps of a row block exchange (NSPLIT == 2)
+  __shared__ float x_max[4][2][16], x_sum[4][2][16];
+  __shared__ uint4 x_p[4][2][32];
+  auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + rb) : "memory"); };
+  constexpr int SN = NSPLIT == 2 ? 1 : 2;          // blocks of 16 keys whose scores this warp computes
 
   for (int kt = 0; kt < n_tiles; ++kt) {
     if (kt + 1 < n_tiles) load_keys(kt + 1, (kt + 1) & 1);
@@ -120,9 +127,9 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     __syncthreads();
     if (active) {
       const unsigned char* kst = k_s + (size_t)(kt & 1) * BN * PITCH;
-      float s[4][4];
+      float s[2 * SN][4];
 #pragma unroll
-      for (int n = 0; n < 4; ++n)
+      for (int n = 0; n < 2 * SN; ++n)
 #pragma unroll
         for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
 #pragma unroll 4
@@ -130,20 +137,21 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         uint32_t a[4];
         ldmatrix_x4(a, q_s + (rb * 16 + (lane & 15)) * PITCH + (k0 + (lane >> 4) * 8) * 2);
 #pragma unroll
-        for (int np = 0; np < 2; ++np) {
+        for (int i = 0; i < SN; ++i) {
+          const int np = NSPLIT == 2 ? cs : i;
           uint32_t b[4];
           ldmatrix_x4(b, kst + (np * 16 + (lane & 7) + ((lane >> 4) << 3)) * PITCH + (k0 + ((lane >> 3) & 1) * 8) * 2);
-          mma_16816(s[2 * np], a, b[0], b[1]);
-          mma_16816(s[2 * np + 1], a, b[2], b[3]);
+          mma_16816(s[2 * i], a, b[0], b[1]);
+          mma_16816(s[2 * i + 1], a, b[2], b[3]);
         }
       }
       const int kbase = k_begin + kt * BN;
       float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-      for (int n = 0; n < 4; ++n)
+      for (int n = 0; n < 2 * SN; ++n)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int key = kbase + n * 8 + 2 * tig + (e & 1);
+          const int key = kbase + (NSPLIT == 2 ? cs * 16 : 0) + n * 8 + 2 * tig + (e & 1);
           const int qp = e < 2 ? qpos0 : qpos1;
           const float t = (key > qp || key >= k_end) ? -INFINITY : s[n][e] * sc;
           s[n][e] = t;
@@ -153,6 +161,15 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      if (NSPLIT == 2) {
+        if (tig == 0) {
+          x_max[rb][cs][g] = mx0;
+          x_max[rb][cs][g + 8] = mx1;
+        }
+        pair_sync();
+        mx0 = fmaxf(mx0, x_max[rb][cs ^ 1][g]);
+        mx1 = fmaxf(mx1, x_max[rb][cs ^ 1][g + 8]);
+      }
       const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
       const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
       const float c0 = fast_exp2(m0 - ms0), c1 = fast_exp2(m1 - ms1);      // m = -inf: 0
@@ -160,7 +177,7 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       m1 = mn1;
       float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
-      for (int n = 0; n < 4; ++n) {
+      for (int n = 0; n < 2 * SN; ++n) {
         s[n][0] = fast_exp2(s[n][0] - ms0);
         s[n][1] = fast_exp2(s[n][1] - ms0);
         s[n][2] = fast_exp2(s[n][2] - ms1);
@@ -174,13 +191,24 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       for (int n = 0; n < VCOLS / 8; ++n) {
         o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1;
       }
+      if (NSPLIT == 2) {      // this warp's probabilities, as the A fragment of its 16 keys, for its partner
+        x_p[rb][cs][lane] = make_uint4(pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
+                                       pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3]));
+        pair_sync();
+      }
 #pragma unroll
       for (int kb = 0; kb < 2; ++kb) {
         uint32_t a[4];
-        a[0] = pack_bf16(s[2 * kb][0], s[2 * kb][1]);
-        a[1] = pack_bf16(s[2 * kb][2], s[2 * kb][3]);
-        a[2] = pack_bf16(s[2 * kb + 1][0], s[2 * kb + 1][1]);
-        a[3] = pack_bf16(s[2 * kb + 1][2], s[2 * kb + 1][3]);
+        if (NSPLIT == 2 && kb != cs) {
+          const uint4 other = x_p[rb][cs ^ 1][lane];
+          a[0] = other.x; a[1] = other.y; a[2] = other.z; a[3] = other.w;
+        } else {
+          const int i = NSPLIT == 2 ? 0 : kb;
+          a[0] = pack_bf16(s[2 * i][0], s[2 * i][1]);
+          a[1] = pack_bf16(s[2 * i][2], s[2 * i][3]);
+          a[2] = pack_bf16(s[2 * i + 1][0], s[2 * i + 1][1]);
+          a[3] = pack_bf16(s[2 * i + 1][2], s[2 * i + 1][3]);
+        }
 #pragma unroll
         for (int cp = 0; cp < VCOLS / 16; ++cp) {
           uint32_t b[4];
@@ -199,6 +227,15 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if (NSPLIT == 2) {          // each warp has summed over its own keys
+    if (tig == 0) {
+      x_sum[rb][cs][g] = l0;
+      x_sum[rb][cs][g + 8] = l1;
+    }
+    pair_sync();
+    l0 += x_sum[rb][cs ^ 1][g];
+    l1 += x_sum[rb][cs ^ 1][g + 8];
+  }
   const size_t gr0 = grow0 + rb * 16 + g, gr1 = gr0 + 8;
   if (splits == 1) {
     const float inv0 = l0 > 0.f ? 1.0f / l0 : 0.f, inv1 = l1 > 0.f ? 1.0f / l1 : 0.f;
