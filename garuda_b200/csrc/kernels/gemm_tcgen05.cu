@@ -58,7 +58,10 @@ constexpr int SMEM_BUDGET_DUAL = 140 * 1024;    // few tokens, gate and up toget
 
 // EPI_ACCUMULATE_NORM: accumulate, and fold in the first half of the norm that follows (EpilogueArgs::h_out);
 // chosen by the host, a variant of its own so that the plain accumulation's code stays as it is
-enum Epilogue : int { EPI_STORE = 0, EPI_ACCUMULATE = 1, EPI_SWIGLU = 2, EPI_ROPE = 3, EPI_ACCUMULATE_NORM = 4 };
+enum Epilogue : int { EPI_STORE = 0, EPI_ACCUMULATE = 1, EPI_SWIGLU = 2, EPI_ROPE = 3, EPI_ACCUMULATE_NORM = 4,
+                      // a flag on EPI_ACCUMULATE (out += alpha * product) and EPI_SWIGLU (the activation is chosen at run
+                      // time): instances of their own, so that the plain ones pay nothing for it
+                      EPI_GENERAL = 8 };
 
 // What the epilogues need beyond the output pointer. For the query/key/value epilogue: the output features are (heads + 2 kv_heads) heads of
 // head_dim; query and key heads are rotated at the token's position (garuda/src/simd/mod.rs:196-206,
@@ -132,7 +135,7 @@ __device__ __forceinline__ __nv_bfloat16* rope_destination(const EpilogueArgs& r
 
 // Bytes of the rotation's tables in the few-token kernel: cosines and sines [BN tokens][64
 // frequencies] and each token's row in the pools.
-__host__ __device__ constexpr int rope_table_bytes(int epi, int bn) { return epi == EPI_ROPE ? bn * 64 * 8 + bn * 8 : 0; }
+__host__ __device__ constexpr int rope_table_bytes(int epi, int bn) { return (epi & 7) == EPI_ROPE ? bn * 64 * 8 + bn * 8 : 0; }
 
 template <int BN, bool DUAL_M, bool DUAL_N, bool TRANS = false, int EXTRA = 0>
 struct Geometry {
@@ -411,7 +414,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
     // instructions). Positions, request rows and block tables are written by copies that end
     // before the first kernel of a chain starts, so they are read without waiting for the kernel
     // in front. The table is complete for every thread after the first barrier of the loop below.
-    constexpr bool ROPE_EARLY = EPI == EPI_ROPE;
+    constexpr bool ROPE_EARLY = (EPI & 7) == EPI_ROPE;
     float (*rope_cs)[64] = reinterpret_cast<float (*)[64]>(smem_raw + (tiles - smem_u32(smem_raw)) + pipe_bytes);
     float (*rope_sn)[64] = rope_cs + BN;
     long long* rope_slot = reinterpret_cast<long long*>(rope_sn + BN);   // element offset of the token's row, head 0; -1: no page
@@ -445,8 +448,8 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
         rope_slot[t] = slot;
       }
     }
-    constexpr bool emit = EPI == EPI_ACCUMULATE_NORM;                    // the norm behind this product is folded in
-    constexpr bool ADD = EPI == EPI_ACCUMULATE || emit;
+    constexpr bool emit = (EPI & 7) == EPI_ACCUMULATE_NORM;                    // the norm behind this product is folded in
+    constexpr bool ADD = (EPI & 7) == EPI_ACCUMULATE || emit;
     float old[ADD ? BN : 1];                 // of this rank's chunks, in their order
     // each epilogue warp's sum of squares per token, in the pipeline's memory (idle by then; static
     // shared memory is kept small, so that two CTAs still fit on an SM)
@@ -563,7 +566,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] *= inv_s[c + j];
           }
-          if (EPI == EPI_SWIGLU) {
+          if ((EPI & 7) == EPI_SWIGLU) {
             if (row_in_tile >= 64) {
 #pragma unroll
               for (int j = 0; j < 16; ++j) xch[j * 64 + row_in_tile - 64] = v[j];
@@ -575,11 +578,11 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
               for (int j = 0; j < 16; ++j) {
                 const int col = n0 + c + j;      // token
                 if (col < rows_n)
-                  store_value<OT>(out + (size_t)col * ldo + feature, gate_fast(ra, v[j], xch[j * 64 + row_in_tile]));
+                  store_value<OT>(out + (size_t)col * ldo + feature, ((EPI & EPI_GENERAL) ? gate_fast(ra, v[j], xch[j * 64 + row_in_tile]) : silu_gate_fast(v[j], xch[j * 64 + row_in_tile])));
               }
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");      // before the next chunk reuses the buffer
-          } else if (EPI == EPI_ROPE) {
+          } else if ((EPI & 7) == EPI_ROPE) {
             // A rotation pairs two rows of the tile (channels i and i + head_dim / 2 of a head, or
             // 2i and 2i + 1): every thread shows its values, then computes its own rotated channel.
 #pragma unroll
@@ -620,7 +623,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
               sq[j] = 0.f;
               if (row >= rows_m || col >= rows_n) continue;
               float x = v[j];
-              if (ADD) x = fmaf(ra.alpha, x, old[ADD ? q * 16 + j : 0]);
+              if (ADD) x = (EPI & EPI_GENERAL) ? fmaf(ra.alpha, x, old[ADD ? q * 16 + j : 0]) : x + old[ADD ? q * 16 + j : 0];
               store_value<OT>(out + (size_t)col * ldo + row, x);
               if (emit) {
                 ra.h_out[(size_t)col * ldo + row] = __float2bfloat16_rn(x * w_row);
@@ -657,11 +660,11 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
 // Epilogue warps of the many-token kernels: two per lane quarter, each with half of a tile's columns
 // (twice the loads and stores in flight), except for the rotation's epilogue, whose threads need
 // whole heads and many registers.
-__host__ __device__ constexpr int epilogue_warps(int epi) { return epi == EPI_ROPE ? 4 : 8; }
+__host__ __device__ constexpr int epilogue_warps(int epi) { return (epi & 7) == EPI_ROPE ? 4 : 8; }
 __host__ __device__ constexpr int p_threads(int epi) { return 64 + 32 * epilogue_warps(epi); }
 // The columns [begin, end) of a BN-wide tile for the first or second warp of a quarter.
 __device__ __forceinline__ void epilogue_columns(int epi, int bn, int which, int& begin, int& end) {
-  const int unit = epi == EPI_SWIGLU ? 128 : 32;
+  const int unit = (epi & 7) == EPI_SWIGLU ? 128 : 32;
   const int mid = epilogue_warps(epi) == 4 ? bn : ((bn / 2 + unit - 1) / unit) * unit;
   begin = which == 0 ? 0 : mid;
   end = which == 0 ? mid : bn;
@@ -703,7 +706,7 @@ __device__ __forceinline__ void epilogue_store16<__nv_bfloat16>(__nv_bfloat16* p
 template <int BN, int EPI, typename OT>
 __device__ __forceinline__ void epilogue_prefetch(float (&first)[32], int row, int n0, const OT* __restrict__ out, int ldo,
                                                   int rows_m, int rows_n, int c_begin) {
-  if ((EPI != EPI_ACCUMULATE && EPI != EPI_ACCUMULATE_NORM) || n0 + BN > rows_n) return;
+  if (((EPI & 7) != EPI_ACCUMULATE && (EPI & 7) != EPI_ACCUMULATE_NORM) || n0 + BN > rows_n) return;
   const int lane = threadIdx.x & 31;
   const int row0 = row - lane;
   const int rows_valid = min(32, rows_m - row0);
@@ -732,18 +735,18 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
                                               int c_begin, int c_end, const float (&first)[32], const float inv) {
   // EMIT: the norm behind this accumulating product is folded in. Every warp writes the sum of squares
   // of its columns of every token into a row of its own of sums_out (two rows per tile of BN columns).
-  constexpr bool EMIT = EPI == EPI_ACCUMULATE_NORM;
+  constexpr bool EMIT = (EPI & 7) == EPI_ACCUMULATE_NORM;
   const int sums_row = 2 * (n0 / BN) + (c_begin != 0 ? 1 : 0);
   // Whole tiles, the usual case: 32 columns at a time, turned round in shared memory. A thread holds
   // a row of the accumulator, so stores straight from its registers touch 32 different lines per
   // instruction; after the turn a warp's instruction covers 32 consecutive columns of one row, and
   // the residual of all 32 rows is asked for before any of it is used.
-  if ((EPI == EPI_STORE || EPI == EPI_ACCUMULATE || EMIT) && n0 + BN <= rows_n) {
+  if (((EPI & 7) == EPI_STORE || (EPI & 7) == EPI_ACCUMULATE || EMIT) && n0 + BN <= rows_n) {
     const int lane = threadIdx.x & 31;
     const int row0 = row - lane;                               // the warp's first row
     const int rows_valid = min(32, rows_m - row0);             // may be <= 0
     OT* gbase = out + (size_t)row0 * ldo + n0 + lane;
-    constexpr bool ACC = EPI == EPI_ACCUMULATE || EMIT;
+    constexpr bool ACC = (EPI & 7) == EPI_ACCUMULATE || EMIT;
     float ssq = 0.f;                                           // EMIT: of the token row0 + lane
     __nv_bfloat16* hbase = EMIT ? ra.h_out + (size_t)row0 * ldo + n0 + lane : nullptr;
     // the residual of a block is asked for one block ahead; the first block's before the tile's
@@ -777,7 +780,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
 #pragma unroll
       for (int rr = 0; rr < 32; ++rr) {
         float v = turn[rr * 33 + lane];
-        if (ACC) v = fmaf(ra.alpha, v, old_cur[ACC ? rr : 0]);
+        if (ACC) v = (EPI & EPI_GENERAL) ? fmaf(ra.alpha, v, old_cur[ACC ? rr : 0]) : v + old_cur[ACC ? rr : 0];
         if (rr < rows_valid) store_value<OT>(gbase + (size_t)rr * ldo + c, v);
         if (EMIT) {
           // the squares go back the way the values came: each lane then adds up its own token's
@@ -795,7 +798,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
     if (EMIT && row < rows_m) ra.sums_out[(size_t)sums_row * ra.sums_ld + row] = ssq;
     return;
   }
-  if (EPI == EPI_SWIGLU && vec && (n0 >> 1) + BN / 2 <= rows_n) {
+  if ((EPI & 7) == EPI_SWIGLU && vec && (n0 >> 1) + BN / 2 <= rows_n) {
     // columns [128 q, 128 q + 64) of the tile are gate values, the next 64 the up values of the same
     // 64 features; 32 features at a time, 16-byte stores from the thread's own row
     const bool row_ok = row < rows_m;
@@ -814,7 +817,8 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
           float v[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j)
-            v[j] = gate_fast(ra, __uint_as_float(g_[h * 16 + j]) * inv, __uint_as_float(u_[h * 16 + j]) * inv);
+            v[j] = (EPI & EPI_GENERAL) ? gate_fast(ra, __uint_as_float(g_[h * 16 + j]) * inv, __uint_as_float(u_[h * 16 + j]) * inv)
+                                       : silu_gate_fast(__uint_as_float(g_[h * 16 + j]) * inv, __uint_as_float(u_[h * 16 + j]) * inv);
           epilogue_store16<OT>(prow + q * 64 + c + h * 16, v, true);
         }
       }
@@ -825,7 +829,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
     if (EMIT && row < rows_m) ra.sums_out[(size_t)sums_row * ra.sums_ld + row] = 0.f;
     return;
   }
-  if (EPI == EPI_ROPE) {
+  if ((EPI & 7) == EPI_ROPE) {
     // This thread holds one token's row: whole heads, so both channels of every rotation pair.
     const int hd = ra.head_dim, half = hd >> 1;
     const bool token_ok = row < rows_m;
@@ -880,7 +884,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
         }
       }
     }
-  } else if (EPI == EPI_SWIGLU) {
+  } else if ((EPI & 7) == EPI_SWIGLU) {
     // columns [128 q, 128 q + 64) of the tile are gate values, the next 64 the up values of
     // the same features: feature = 64 * (packed row / 128) + offset
 #pragma unroll 1
@@ -895,7 +899,9 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
         if (row >= rows_m || col >= rows_n) continue;
         float v[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = gate_fast(ra, __uint_as_float(r0[j]) * inv, __uint_as_float(r1[j]) * inv);
+        for (int j = 0; j < 16; ++j)
+          v[j] = (EPI & EPI_GENERAL) ? gate_fast(ra, __uint_as_float(r0[j]) * inv, __uint_as_float(r1[j]) * inv)
+                                     : silu_gate_fast(__uint_as_float(r0[j]) * inv, __uint_as_float(r1[j]) * inv);
         OT* p = out + (size_t)row * ldo + col;
         if (col + 16 <= rows_n) {
           epilogue_store16<OT>(p, v, vec);
@@ -919,7 +925,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
     OT* p = out + (size_t)row * ldo + col;
     if (EMIT) {
       for (int j = 0; j < 16 && col + j < rows_n; ++j) {
-        const float x = fmaf(ra.alpha, v[j], gb::to_float<OT>(p[j]));
+        const float x = v[j] + gb::to_float<OT>(p[j]);
         store_value<OT>(p + j, x);
         ra.h_out[(size_t)row * ldo + col + j] = __float2bfloat16_rn(x * ra.weight[col + j]);
         ssq += x * x;
@@ -927,24 +933,28 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
       continue;
     }
     if (col + 16 <= rows_n) {
-      if (EPI == EPI_ACCUMULATE) {
+      if ((EPI & 7) == EPI_ACCUMULATE) {
         if (vec) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float4 old = reinterpret_cast<const float4*>(p)[i];
-            v[4 * i] = fmaf(ra.alpha, v[4 * i], old.x); v[4 * i + 1] = fmaf(ra.alpha, v[4 * i + 1], old.y);
-            v[4 * i + 2] = fmaf(ra.alpha, v[4 * i + 2], old.z); v[4 * i + 3] = fmaf(ra.alpha, v[4 * i + 3], old.w);
+            if (EPI & EPI_GENERAL) {
+              v[4 * i] = fmaf(ra.alpha, v[4 * i], old.x); v[4 * i + 1] = fmaf(ra.alpha, v[4 * i + 1], old.y);
+              v[4 * i + 2] = fmaf(ra.alpha, v[4 * i + 2], old.z); v[4 * i + 3] = fmaf(ra.alpha, v[4 * i + 3], old.w);
+            } else {
+              v[4 * i] += old.x; v[4 * i + 1] += old.y; v[4 * i + 2] += old.z; v[4 * i + 3] += old.w;
+            }
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = fmaf(ra.alpha, v[j], gb::to_float<OT>(p[j]));
+          for (int j = 0; j < 16; ++j) v[j] = (EPI & EPI_GENERAL) ? fmaf(ra.alpha, v[j], gb::to_float<OT>(p[j])) : v[j] + gb::to_float<OT>(p[j]);
         }
       }
       epilogue_store16<OT>(p, v, vec);
     } else {
       for (int j = 0; j < 16 && col + j < rows_n; ++j) {
         float x = v[j];
-        if (EPI == EPI_ACCUMULATE) x = fmaf(ra.alpha, x, gb::to_float<OT>(p[j]));
+        if ((EPI & 7) == EPI_ACCUMULATE) x = (EPI & EPI_GENERAL) ? fmaf(ra.alpha, x, gb::to_float<OT>(p[j])) : x + gb::to_float<OT>(p[j]);
         store_value<OT>(p + j, x);
       }
     }
@@ -1400,15 +1410,19 @@ int launch_cluster(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ld
 template <int BN>
 int dispatch_cluster(int epi, int out_dtype, const CUtensorMap& mm, const CUtensorMap& mn, void* out, int ldo,
                      int weight_rows, int out_features, int tokens, int K, cudaStream_t stream, const EpilogueArgs& ra) {
-  if (epi == EPI_STORE) {
+  if ((epi & 7) == EPI_STORE) {
     if (out_dtype == GB_F32)
       return launch_cluster<BN, EPI_STORE, float>(mm, mn, (float*)out, ldo, weight_rows, out_features, tokens, K, stream, ra);
     return launch_cluster<BN, EPI_STORE, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, ldo, weight_rows, out_features, tokens, K, stream, ra);
   }
-  if (epi == EPI_ACCUMULATE && ra.h_out != nullptr)
+  if ((epi & 7) == EPI_ACCUMULATE && ra.h_out != nullptr)
     return launch_cluster<BN, EPI_ACCUMULATE_NORM, float>(mm, mn, (float*)out, ldo, weight_rows, out_features, tokens, K, stream, ra);
-  if (epi == EPI_ACCUMULATE)
+  if ((epi & 7) == EPI_ACCUMULATE && ra.alpha != 1.0f)
+    return launch_cluster<BN, EPI_ACCUMULATE | EPI_GENERAL, float>(mm, mn, (float*)out, ldo, weight_rows, out_features, tokens, K, stream, ra);
+  if ((epi & 7) == EPI_ACCUMULATE)
     return launch_cluster<BN, EPI_ACCUMULATE, float>(mm, mn, (float*)out, ldo, weight_rows, out_features, tokens, K, stream, ra);
+  if (ra.gate_act != GATE_SILU)
+    return launch_cluster<BN, EPI_SWIGLU | EPI_GENERAL, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, ldo, weight_rows, out_features, tokens, K, stream, ra);
   return launch_cluster<BN, EPI_SWIGLU, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, ldo, weight_rows, out_features, tokens, K, stream, ra);
 }
 
@@ -1479,7 +1493,7 @@ bool many_token_pairs(int tokens, int weight_rows, int epi = -1) {
   // pairs' 256 x 256 tiles need fewer rounds: a round of pairs costs a CTA as much as a round of 128-wide
   // tiles (1 MB of operands for each), so 512 tokens times 11,264 packed rows are two rounds of pairs
   // against three (a step of 512 tokens 3.35 to 3.1 ms). The other products have one round either way.
-  if (epi != EPI_SWIGLU || tokens <= few_token_limit()) return false;
+  if ((epi & 7) != EPI_SWIGLU || tokens <= few_token_limit()) return false;
   const int sms = sm_count(), pairs = sms / 2;
   const int pair_tiles = ((tokens + 2 * BM - 1) / (2 * BM)) * ((weight_rows + 255) / 256);
   const int pair_cost = ((pair_tiles + pairs - 1) / pairs) * 128;
@@ -1587,11 +1601,11 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
                          const GbNormFold* norm, float alpha, int gate_act, float gate_limit, cudaStream_t stream) {
   if (!gb_gemm_tc_supported(x, w, Mx, Nw, K))
     return gb::fail(GB_UNSUPPORTED, "gemm_tc: needs K a multiple of 8 and 16-byte aligned operands (K = %d)", K);
-  if (epi == EPI_ACCUMULATE && out_dtype != GB_F32)
+  if ((epi & 7) == EPI_ACCUMULATE && out_dtype != GB_F32)
     return gb::fail(GB_BAD_ARGUMENT, "gemm_tc: accumulation needs a 32-bit output");
-  if (epi == EPI_SWIGLU && out_dtype != GB_BF16)
+  if ((epi & 7) == EPI_SWIGLU && out_dtype != GB_BF16)
     return gb::fail(GB_BAD_ARGUMENT, "gemm_tc: the SiLU-gate epilogue writes bfloat16");
-  const int weight_rows = epi == EPI_SWIGLU ? 128 * ((Nw + 63) / 64) : Nw;
+  const int weight_rows = (epi & 7) == EPI_SWIGLU ? 128 * ((Nw + 63) / 64) : Nw;
   EpilogueArgs ra{};
   fold_norm(ra, norm);
   take_next_stream(ra);
@@ -1599,7 +1613,7 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
   ra.alpha = alpha;
   ra.gate_act = gate_act;
   ra.gate_limit = gate_limit;
-  if (ra.h_out != nullptr && epi != EPI_ACCUMULATE)
+  if (ra.h_out != nullptr && (epi & 7) != EPI_ACCUMULATE)
     return gb::fail(GB_UNSUPPORTED, "gemm_tc: a norm is folded in behind accumulating products only (epilogue %d)", epi);
   CUtensorMap mm, mn;
   int rc;
@@ -1618,11 +1632,15 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
   if ((rc = tensor_map_2d(w, weight_rows, K, pairs ? 128 : width, &mn))) return rc;
 #define GB_MANY(LAUNCH, BN_)                                                                                          \
   do {                                                                                                                \
-    if (epi == EPI_SWIGLU)                                                                                            \
+    if ((epi & 7) == EPI_SWIGLU && ra.gate_act != GATE_SILU)                                                          \
+      return LAUNCH<BN_, EPI_SWIGLU | EPI_GENERAL, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows, Nw, K, stream, ra); \
+    if ((epi & 7) == EPI_SWIGLU)                                                                                      \
       return LAUNCH<BN_, EPI_SWIGLU, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows, Nw, K, stream, ra); \
-    if (epi == EPI_ACCUMULATE && ra.h_out != nullptr)                                                                 \
+    if ((epi & 7) == EPI_ACCUMULATE && ra.h_out != nullptr)                                                                 \
       return LAUNCH<BN_, EPI_ACCUMULATE_NORM, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream, ra);    \
-    if (epi == EPI_ACCUMULATE)                                                                                        \
+    if ((epi & 7) == EPI_ACCUMULATE && ra.alpha != 1.0f)                                                              \
+      return LAUNCH<BN_, EPI_ACCUMULATE | EPI_GENERAL, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream, ra); \
+    if ((epi & 7) == EPI_ACCUMULATE)                                                                                  \
       return LAUNCH<BN_, EPI_ACCUMULATE, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream, ra);         \
     if (out_dtype == GB_F32)                                                                                          \
       return LAUNCH<BN_, EPI_STORE, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream, ra);              \
