@@ -22,15 +22,12 @@ namespace {
 // One block per token. src row: [latent(rank) | rot part(rot)] in 32-bit, `row_stride` apart.
 // The first `rot_dims` channels of the rot part are turned in pairs (2i, 2i + 1) by pos * inv_freq[i].
 template <typename WT, typename OT>
-__global__ void __launch_bounds__(128)
-latent_append_kernel(const float* __restrict__ src, int row_stride, const WT* __restrict__ norm_w, float eps,
-                     int rank, int rot, int rot_dims, const float* __restrict__ inv_freq,
-                     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_req,
-                     const int32_t* __restrict__ block_table, int table_width, int page_size,
-                     OT* __restrict__ pool) {
-  gb::pdl_launch_dependents();
-  gb::pdl_wait();
-  __shared__ float part[4];
+__device__ __forceinline__ void append_row(const float* __restrict__ src, int row_stride, const WT* __restrict__ norm_w,
+                                           float eps, int rank, int rot, int rot_dims, const float* __restrict__ inv_freq,
+                                           const int32_t* __restrict__ positions, const int32_t* __restrict__ token_req,
+                                           const int32_t* __restrict__ block_table, int table_width, int page_size,
+                                           OT* __restrict__ pool) {
+  __shared__ float part[8];
   __shared__ float inv_s;
   const int t = blockIdx.x;
   const float* s = src + (size_t)t * row_stride;
@@ -41,7 +38,11 @@ latent_append_kernel(const float* __restrict__ src, int row_stride, const WT* __
   ss = gb::warp_sum(ss);
   if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
   __syncthreads();
-  if (threadIdx.x == 0) inv_s = 1.0f / sqrtf((part[0] + part[1] + part[2] + part[3]) / (float)rank + eps);
+  if (threadIdx.x == 0) {
+    float total = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) total += part[w];      // the warps' sums in a fixed order
+    inv_s = 1.0f / sqrtf(total / (float)rank + eps);
+  }
   __syncthreads();
   if (page < 0) return;      // a padding row, or a step the host should have refused: nothing is stored
   const float inv = inv_s;
@@ -59,17 +60,28 @@ latent_append_kernel(const float* __restrict__ src, int row_stride, const WT* __
   for (int c = rot_dims + threadIdx.x; c < rot; c += blockDim.x) dst[rank + c] = gb::from_float<OT>(r[c]);
 }
 
+template <typename WT, typename OT>
+__global__ void __launch_bounds__(128)
+latent_append_kernel(const float* __restrict__ src, int row_stride, const WT* __restrict__ norm_w, float eps,
+                     int rank, int rot, int rot_dims, const float* __restrict__ inv_freq,
+                     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_req,
+                     const int32_t* __restrict__ block_table, int table_width, int page_size,
+                     OT* __restrict__ pool) {
+  gb::pdl_launch_dependents();
+  gb::pdl_wait();
+  append_row<WT, OT>(src, row_stride, norm_w, eps, rank, rot, rot_dims, inv_freq, positions, token_req, block_table,
+                     table_width, page_size, pool);
+}
+
 // One block per token. src row: H heads of [unrotated (dn) | rotated part (rot)] in 32-bit. The
 // unrotated parts go to q_nope [T, H, dn]; the rotated parts, turned like the keys' (pairs
 // (2i, 2i + 1) of the first rot_dims channels by pos * inv_freq[i]), go to the last `rot` channels of
 // q_lat's rows [T, H, lat_row], whose first channels a product fills afterwards.
 template <typename OT>
-__global__ void __launch_bounds__(256)
-latent_query_prepare_kernel(const float* __restrict__ src, int row_stride, int H, int dn, int rot, int rot_dims,
-                            const float* __restrict__ inv_freq, const int32_t* __restrict__ positions,
-                            OT* __restrict__ q_nope, OT* __restrict__ q_lat, int lat_row) {
-  gb::pdl_launch_dependents();
-  gb::pdl_wait();
+__device__ __forceinline__ void prepare_query(const float* __restrict__ src, int row_stride, int H, int dn, int rot,
+                                              int rot_dims, const float* __restrict__ inv_freq,
+                                              const int32_t* __restrict__ positions, OT* __restrict__ q_nope,
+                                              OT* __restrict__ q_lat, int lat_row) {
   const int t = blockIdx.x;
   const float* s = src + (size_t)t * row_stride;
   const int pos = positions[t];
@@ -93,6 +105,32 @@ latent_query_prepare_kernel(const float* __restrict__ src, int row_stride, int H
     const int h = e / rest, c = rot_dims + e % rest;
     q_lat[((size_t)t * H + h) * lat_row + (lat_row - rot) + c] = gb::from_float<OT>(s[h * hw + dn + c]);
   }
+}
+
+template <typename OT>
+__global__ void __launch_bounds__(256)
+latent_query_prepare_kernel(const float* __restrict__ src, int row_stride, int H, int dn, int rot, int rot_dims,
+                            const float* __restrict__ inv_freq, const int32_t* __restrict__ positions,
+                            OT* __restrict__ q_nope, OT* __restrict__ q_lat, int lat_row) {
+  gb::pdl_launch_dependents();
+  gb::pdl_wait();
+  prepare_query<OT>(src, row_stride, H, dn, rot, rot_dims, inv_freq, positions, q_nope, q_lat, lat_row);
+}
+
+// Both at once for a step's rows [queries (H * (dn + rot)) | latent (rank) | key part (rot)]: the
+// queries prepared and the cache row written by one block per token.
+template <typename WT, typename OT>
+__global__ void __launch_bounds__(256)
+latent_rows_kernel(const float* __restrict__ src, int row_stride, int H, int dn, int rot, int rot_dims,
+                   const float* __restrict__ inv_freq, const int32_t* __restrict__ positions, OT* __restrict__ q_nope,
+                   OT* __restrict__ q_lat, const WT* __restrict__ norm_w, float eps, int rank,
+                   const int32_t* __restrict__ token_req, const int32_t* __restrict__ block_table, int table_width,
+                   int page_size, OT* __restrict__ pool) {
+  gb::pdl_launch_dependents();
+  gb::pdl_wait();
+  prepare_query<OT>(src, row_stride, H, dn, rot, rot_dims, inv_freq, positions, q_nope, q_lat, rank + rot);
+  append_row<WT, OT>(src + (size_t)H * (dn + rot), row_stride, norm_w, eps, rank, rot, rot_dims, inv_freq, positions,
+                     token_req, block_table, table_width, page_size, pool);
 }
 
 // out[t][h][n] = sum_k a[t][h][k] * w_h[n][k], n < N, and out[t][h][N + j] = a[t][h][K + j], j < tail.
@@ -185,6 +223,26 @@ GB_EXPORT int gb_latent_query_prepare(const float* src, int row_stride, int H, i
         gb::launch_pdl(latent_query_prepare_kernel<OT>, dim3(T), dim3(256), 0, stream, dim3(1, 1, 1), src, row_stride, H, dn,
                        rot, rot_dims, inv_freq, positions, (OT*)q_nope, (OT*)q_lat, lat_row),
         "latent_query_prepare");
+  });
+}
+
+GB_EXPORT int gb_latent_rows(const float* src, int row_stride, int H, int dn, int rot, int rot_dims,
+                             const float* inv_freq, const int32_t* positions, void* q_nope, void* q_lat,
+                             const void* norm_w, int w_dtype, float eps, int rank, const int32_t* token_req,
+                             const int32_t* block_table, int table_width, int page_size, void* pool, int out_dtype,
+                             int T, cudaStream_t stream) {
+  if (T <= 0) return GB_OK;
+  if (H < 1 || dn < 1 || rank < 1 || rot < 0 || rot_dims < 0 || rot_dims > rot || rot_dims % 2)
+    return gb::fail(GB_BAD_ARGUMENT, "latent_rows: heads %d, %d + %d channels of which %d turned, rank %d", H, dn, rot, rot_dims, rank);
+  if (rot_dims > 0 && !inv_freq) return gb::fail(GB_BAD_ARGUMENT, "latent_rows: a rotation without frequencies");
+  return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
+    return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
+      return gb::check_pdl_launch(
+          gb::launch_pdl(latent_rows_kernel<WT, OT>, dim3(T), dim3(256), 0, stream, dim3(1, 1, 1), src, row_stride, H, dn, rot,
+                         rot_dims, inv_freq, positions, (OT*)q_nope, (OT*)q_lat, (const WT*)norm_w, eps, rank, token_req,
+                         block_table, table_width, page_size, (OT*)pool),
+          "latent_rows");
+    });
   });
 }
 

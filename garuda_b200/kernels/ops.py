@@ -179,6 +179,9 @@ class CudaOps:
                                 c_int, c_int, c_int, c_int, c_void_p],
             "gb_latent_query_prepare": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                         c_void_p, c_int, c_int, c_int, c_void_p],
+            "gb_latent_rows": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_void_p, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
+                               c_void_p],
     }
 
     def _stream(self):
@@ -655,6 +658,28 @@ class CudaOps:
             src.data_ptr(), src.stride(0), int(heads), int(dn), int(rot), int(dims), _ptr(inv), positions.data_ptr(),
             q_nope.data_ptr(), q_lat.data_ptr(), _tag(q_lat, "q_lat"), q_lat.shape[2], T, self._stream()),
             "latent_query_prepare")
+
+    def latent_rows(self, src, heads, dn, rot, rank, rotary, positions, q_nope, q_lat, norm_w, eps, token_req,
+                    block_table, pool, page_size):
+        """``latent_query_prepare`` and ``latent_append`` in one kernel, for a step's 32-bit rows
+        ``src [T, heads * (dn + rot) + rank + rot]``: queries first, then the latent and its key part."""
+        self._on_device(src, positions, q_nope, q_lat, norm_w, token_req, block_table, pool)
+        T = src.shape[0]
+        _need(src.dtype == torch.float32 and src.is_contiguous() and src.shape[1] == heads * (dn + rot) + rank + rot,
+              "latent_rows: src")
+        _need(q_nope.is_contiguous() and q_lat.is_contiguous() and q_nope.dtype == q_lat.dtype == pool.dtype
+              and tuple(q_nope.shape) == (T, heads, dn) and tuple(q_lat.shape) == (T, heads, rank + rot), "latent_rows: outputs")
+        _need(pool.is_contiguous() and tuple(pool.shape[1:]) == (1, page_size, rank + rot), "latent_rows: pool shape")
+        _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "latent_rows: block table")
+        inv, dims = None, 0
+        if rotary is not None:
+            _need(rotary.interleaved and rotary.head_dim <= rot, "latent_rows: pairs (2i, 2i + 1) within the rotated part")
+            inv, dims = self.inv_freq(rotary), rotary.head_dim
+        self._check(self.mixers, self.mixers.gb_latent_rows(
+            src.data_ptr(), src.stride(0), int(heads), int(dn), int(rot), int(dims), _ptr(inv), positions.data_ptr(),
+            q_nope.data_ptr(), q_lat.data_ptr(), norm_w.data_ptr(), _tag(norm_w, "latent norm"), float(eps), int(rank),
+            token_req.data_ptr(), block_table.data_ptr(), block_table.shape[1], int(page_size), pool.data_ptr(),
+            _tag(pool, "latent pool"), T, self._stream()), "latent_rows")
 
     def head_linear(self, a, w, out, n, k, transposed: bool, tail: int = 0):
         """One small product per head: ``out[t, h, :n] = a[t, h, :k] @ w_h^T`` and

@@ -93,13 +93,16 @@ class LatentAttention(Mixer):
         T, H = h.shape[0], self.heads
         qd = ws.get("latent_qd", (T, self.q_width + self.row), torch.float32)
         ops.linear(h, self.w_qd, qd)
-        if cache.writes:
-            ops.latent_append(qd[:, self.q_width:], self.norm_w, self.eps, self.rank, self.rot_dim, self.rotary,
-                              b.positions, b.token_req, cache.block_table, cache.k, cache.page_size)
         # the query in the latent's coordinates: [W_uk^T q^n | q^r]
         q_lat = ws.get("latent_q", (T, H, self.row), self.dtype)
         q_nope = ws.get("latent_q_nope", (T, H, self.dim), self.dtype)
-        ops.latent_query_prepare(qd[:, :self.q_width], H, self.dim, self.rot_dim, self.rotary, b.positions, q_nope, q_lat)
+        if cache.writes:
+            # one kernel: the queries prepared, the step's cache rows normed, rotated and written
+            ops.latent_rows(qd, H, self.dim, self.rot_dim, self.rank, self.rotary, b.positions, q_nope, q_lat,
+                            self.norm_w, self.eps, b.token_req, cache.block_table, cache.k, cache.page_size)
+        else:
+            ops.latent_query_prepare(qd[:, :self.q_width], H, self.dim, self.rot_dim, self.rotary, b.positions,
+                                     q_nope, q_lat)
         ops.head_linear(q_nope, self.w_uk_t, q_lat, n=self.rank, k=self.dim, transposed=False)
         mixed = ws.get("latent_ctx", (T, H * self.rank), self.dtype)
         ops.paged_attention(q_lat, cache.k, cache.k, cache.block_table, b.cu_q, b.kv_lens, b.token_req, mixed,

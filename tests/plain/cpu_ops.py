@@ -246,6 +246,12 @@ class CpuOps:
             r[..., :d] = self._rotate(r[..., :d], positions, rotary)
         q_lat[..., q_lat.shape[2] - rot:] = r.to(q_lat.dtype)
 
+    def latent_rows(self, src, heads, dn, rot, rank, rotary, positions, q_nope, q_lat, norm_w, eps, token_req,
+                    block_table, pool, page_size):
+        qw = heads * (dn + rot)
+        self.latent_query_prepare(src[:, :qw], heads, dn, rot, rotary, positions, q_nope, q_lat)
+        self.latent_append(src[:, qw:], norm_w, eps, rank, rot, rotary, positions, token_req, block_table, pool, page_size)
+
     def head_linear(self, a, w, out, n, k, transposed, tail=0):
         T, H = a.shape[:2]
         wf = w.float()

@@ -195,6 +195,21 @@ def test_query_rows_prepared_and_mapped_into_the_latent(both, T, H, dn, rot, dim
     cpu.latent_query_prepare(src, H, dn, rot, rp, pos, qn_c, ql_c)
     close(qn, qn_c, dt, "unrotated query parts")
     close(ql, ql_c, dt, "rotated query parts")
+    # the same, with the cache row written by the same kernel
+    ps = 16
+    full = torch.cat([src, rnd(T, rank + rot, seed=2)], dim=1).contiguous()
+    nw = rnd(rank, dtype=dt, seed=3)
+    req = torch.zeros(T, dtype=torch.int32)
+    pages = (7 + T + ps - 1) // ps
+    bt = torch.arange(pages - 1, -1, -1, dtype=torch.int32).view(1, pages)
+    pool_c = torch.zeros(pages, 1, ps, rank + rot, dtype=dt)
+    pool, qn2, ql2 = pool_c.clone().cuda(), torch.zeros_like(qn), torch.zeros_like(ql)
+    qn2_c, ql2_c = torch.zeros_like(qn_c), torch.zeros_like(ql_c)
+    ops.latent_rows(full.cuda(), H, dn, rot, rank, rp, pos.cuda(), qn2, ql2, nw.cuda(), 1e-5, req.cuda(), bt.cuda(), pool, ps)
+    cpu.latent_rows(full, H, dn, rot, rank, rp, pos, qn2_c, ql2_c, nw, 1e-5, req, bt, pool_c, ps)
+    close(qn2, qn2_c, dt, "queries, fused")
+    close(ql2, ql2_c, dt, "rotated query parts, fused")
+    close(pool, pool_c, dt, "cache rows, fused")
     w = rnd(H * rank, dn, dtype=dt, scale=0.3, seed=1)
     ops.head_linear(qn_c.cuda(), w.cuda(), ql, rank, dn, False)
     cpu.head_linear(qn_c, w, ql_c, rank, dn, False)
