@@ -496,7 +496,8 @@ def run_design(args) -> dict:
             h = torch.randn(M, W, device=dev).to(bf)
             x = torch.zeros(M, W, device=dev)
             E, top, F = z["experts"], z["top"], z["expert_ff"]
-            wgu = (torch.randn(E, 2 * F, W, device=dev) * 0.02).to(bf)
+            wgu = ops.pack_expert_gate_up([(torch.randn(F, W, device=dev) * 0.02).to(bf) for _ in range(E)],
+                                          [(torch.randn(F, W, device=dev) * 0.02).to(bf) for _ in range(E)])
             wd = (torch.randn(E, W, F, device=dev) * 0.02).to(bf)
             wr = (torch.randn(E, W, device=dev) * 0.5).to(bf)
             ids = torch.empty(M, top, dtype=torch.int32, device=dev)

@@ -95,6 +95,11 @@ struct EpilogueArgs {
   // CTAs ask for those weights to be brought into L2 meanwhile, each a slice.
   const uint8_t* next_stream;
   long long next_bytes;
+  // A grouped product (the experts of a routed feed-forward): the token rows come sorted by group in
+  // blocks of 128 rows, every block of one group; the weights of all groups are one tensor, a group's
+  // rows one after the other; block_w_row[block] is the first weight row of the block's group (null:
+  // an ordinary product). Only the weight tile's coordinate changes.
+  const int32_t* block_w_row = nullptr;
   // out += alpha * product for the accumulating epilogues (a model's residual multiplier)
   float alpha = 1.0f;
   // the gated epilogue's activation: GATE_SILU silu(g) u; GATE_GELU_TANH gelu_tanh(g) u;
@@ -1034,7 +1039,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
           const uint32_t base = tiles + s * G::STAGE_BYTES;
           mbar_arrive_expect_tx(bar, G::STAGE_BYTES);
           tma_load_2d(base, &map_m, bar, kb * BK, m0);
-          tma_load_2d(base + G::A_BYTES, &map_n, bar, kb * BK, n0);
+          tma_load_2d(base + G::A_BYTES, &map_n, bar, kb * BK, n0 + (ra.block_w_row ? ra.block_w_row[m0 / BM] : 0));
           issued = it + 1;
         }
       }
@@ -1650,6 +1655,49 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
   if (width == 256) GB_MANY(launch_persistent, 256);
   GB_MANY(launch_persistent, 128);
 #undef GB_MANY
+}
+
+// A grouped product on the many-token kernel (one CTA per 128 x BN tile; no CTA pairs, whose 256-row
+// tiles would straddle groups): x [Mx, K] holds the rows sorted by group, every 128-row block of one
+// group (Mx a multiple of 128); w [groups * weight rows, K] the groups' weights one after the other;
+// block_w_row [Mx / 128] (device) the first weight row of each block's group. epi, Nw (one group's
+// output features), alpha and the gate as for gb_gemm_tc; out [Mx, Nw].
+GB_EXPORT int gb_gemm_tc_grouped(const void* x, const void* w, void* out, int Mx, int Nw, int K, int groups,
+                                 const int32_t* block_w_row, int out_dtype, int epi, float alpha, int gate_act,
+                                 float gate_limit, cudaStream_t stream) {
+  if (!gb_gemm_tc_supported(x, w, Mx, Nw, K))
+    return gb::fail(GB_UNSUPPORTED, "gemm_tc_grouped: needs K a multiple of 8 and 16-byte aligned operands (K = %d)", K);
+  if (Mx % BM || Mx <= few_token_limit() || groups < 1 || block_w_row == nullptr)
+    return gb::fail(GB_BAD_ARGUMENT, "gemm_tc_grouped: %d rows in blocks of %d, %d groups", Mx, BM, groups);
+  if (epi != EPI_STORE && epi != EPI_SWIGLU) return gb::fail(GB_UNSUPPORTED, "gemm_tc_grouped: epilogue %d", epi);
+  if (epi == EPI_SWIGLU && out_dtype != GB_BF16)
+    return gb::fail(GB_BAD_ARGUMENT, "gemm_tc_grouped: the gated epilogue writes bfloat16");
+  if (gate_act < GATE_SILU || gate_act > GATE_CLAMPED_SWISH) return gb::fail(GB_BAD_ARGUMENT, "gemm_tc_grouped: gate activation %d", gate_act);
+  const int weight_rows = epi == EPI_SWIGLU ? 128 * ((Nw + 63) / 64) : Nw;
+  if ((long long)groups * weight_rows > 0x7fffffffLL) return gb::fail(GB_UNSUPPORTED, "gemm_tc_grouped: too many weight rows");
+  EpilogueArgs ra{};
+  ra.block_w_row = block_w_row;
+  ra.alpha = alpha;
+  ra.gate_act = gate_act;
+  ra.gate_limit = gate_limit;
+  CUtensorMap mm, mn;
+  int rc;
+  if ((rc = tensor_map_2d(x, Mx, K, BM, &mm))) return rc;
+  const int width = weight_rows >= 256 ? 256 : 128;
+  if ((rc = tensor_map_2d(w, groups * weight_rows, K, width, &mn))) return rc;
+#define GB_GROUPED(BN_)                                                                                                \
+  do {                                                                                                                \
+    if (epi == EPI_SWIGLU && gate_act != GATE_SILU)                                                                   \
+      return launch_persistent<BN_, EPI_SWIGLU | EPI_GENERAL, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows, Nw, K, stream, ra); \
+    if (epi == EPI_SWIGLU)                                                                                            \
+      return launch_persistent<BN_, EPI_SWIGLU, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows, Nw, K, stream, ra); \
+    if (out_dtype == GB_F32)                                                                                          \
+      return launch_persistent<BN_, EPI_STORE, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream, ra);   \
+    return launch_persistent<BN_, EPI_STORE, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows, Nw, K, stream, ra); \
+  } while (0)
+  if (width == 256) GB_GROUPED(256);
+  GB_GROUPED(128);
+#undef GB_GROUPED
 }
 
 // The query/key/value product with the rotation and the cache write in its epilogue:

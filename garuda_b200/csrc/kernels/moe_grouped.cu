@@ -80,7 +80,7 @@ __device__ __forceinline__ float gate_act(int kind, float limit, float g, float 
 // out[row0 + r][n] = sum_k A_e[r][k] * W_e[n][k] for the tile's rows r and columns n0 .. n0 + 63.
 // A_e's row r is a[e * a_group + (gather ? gather[row0 + r] / gather_div : row0 + r) * lda ..];
 // out's row is out[e * out_group + (row0 + r) * ldo ..]. GATED: W_e has N gate rows followed by N up
-// rows, and out (bfloat16) is act(gate, up). With a tile list (tile_expert ...) the CTA reads its
+// rows (or the packed layout, see `packed`), and out (bfloat16) is act(gate, up). With a tile list (tile_expert ...) the CTA reads its
 // group and rows from it; without, blockIdx.z is the group and every group has `rows_all` rows.
 // The CTA is WM x WN warps, a warp's tile (MI * 16) x (NP * 16): 128 x 64 for groups of many rows,
 // 16 x 64 for a few rows per group, where a taller tile would be padding.
@@ -90,7 +90,7 @@ grouped_gemm_kernel(const __nv_bfloat16* __restrict__ a, int lda, long long a_gr
                     int gather_div, const __nv_bfloat16* __restrict__ w, long long w_group, OT* __restrict__ out, int ldo,
                     long long out_group, int N, int K, const int32_t* __restrict__ tile_expert,
                     const int32_t* __restrict__ tile_row0, const int32_t* __restrict__ tile_rows,
-                    const int32_t* __restrict__ num_tiles, int rows_all, int kind, float limit) {
+                    const int32_t* __restrict__ num_tiles, int rows_all, int kind, float limit, int packed) {
   constexpr int TM = WM * MI * 16, TN = WN * NP * 16, THREADS = WM * WN * 32;
   constexpr int BROWS = GATED ? 2 * TN : TN;
   constexpr int CH = GK / 8;                       // 16-byte chunks of a tile's row
@@ -128,7 +128,9 @@ grouped_gemm_kernel(const __nv_bfloat16* __restrict__ a, int lda, long long a_gr
       const int k = k0 + c * 8;
       const int n = n0 + (r % TN);
       const bool valid = n < N && k < K;
-      const size_t wrow = (size_t)(r < TN ? n : N + n);
+      // gate row n and up row n of the group: N gate rows then N up rows, or (packed) gate and up rows
+      // interleaved in groups of 64, which is the layout of the tcgen05 product's gated epilogue
+      const size_t wrow = packed ? (size_t)((n >> 6) * 128 + (n & 63) + (r < TN ? 0 : 64)) : (size_t)(r < TN ? n : N + n);
       cp16(bs + r * GPITCH + c * 16, we + (valid ? wrow * K + k : 0), valid);
     }
   };
@@ -240,11 +242,13 @@ GB_EXPORT long long gb_moe_grouped_index_words(long long R, int E) {
   return 2 * R + 3 * tiles + 4;
 }
 
-// h [T, K], w_gate_up [E, 2F, K], w_down [E, N, F] bfloat16; ids [T, top], weights [T, top]; x [T, N] 32-bit.
+// h [T, K], w_gate_up [E, 2F, K] (packed: [E, 128 * ceil(F / 64), K], gate and up rows in groups of 64),
+// w_down [E, N, F] bfloat16; ids [T, top], weights [T, top]; x [T, N] 32-bit.
 // index: gb_moe_grouped_index_words int32; act: [T * top, F] bfloat16; y: [T * top, N] 32-bit.
 GB_EXPORT int gb_moe_grouped(const void* h, const void* w_gate_up, const void* w_down, const int32_t* ids,
                              const float* weights, float* x, int T, int top, int E, int F, int K, int N, int kind,
-                             float limit, float alpha, int32_t* index, void* act, float* y, cudaStream_t stream) {
+                             float limit, float alpha, int packed, int32_t* index, void* act, float* y,
+                             cudaStream_t stream) {
   if (T <= 0) return GB_OK;
   if (K % 8 || F % 8) return gb::fail(GB_UNSUPPORTED, "moe_grouped: widths %d and %d must be multiples of 8", K, F);
   if (E < 1 || (size_t)E * 2 * sizeof(int32_t) > 40 * 1024) return gb::fail(GB_UNSUPPORTED, "moe_grouped: %d experts", E);
@@ -270,22 +274,106 @@ GB_EXPORT int gb_moe_grouped(const void* h, const void* w_gate_up, const void* w
   const dim3 grid_f((F + GN - 1) / GN, max_tiles), grid_n((N + GN - 1) / GN, max_tiles);
   const int32_t* none = nullptr;
   const int32_t *te = tile_expert, *t0 = tile_row0, *tr = tile_rows, *nt = num_tiles, *rp = row_pair;
-  const long long zero = 0, gu_group = (long long)2 * F * K, d_group = (long long)N * F;
+  const long long zero = 0, gu_group = (long long)(packed ? 128 * ((F + 63) / 64) : 2 * F) * K, d_group = (long long)N * F;
   if (tall)
     rc = launch_grouped<4, 2, 2, 2, true, __nv_bfloat16>(grid_f, stream, "moe_gate_up_grouped", hh, K, zero, rp, top, wgu,
-                                                        gu_group, a, F, zero, F, K, te, t0, tr, nt, 0, kind, limit);
+                                                        gu_group, a, F, zero, F, K, te, t0, tr, nt, 0, kind, limit, packed);
   else
     rc = launch_grouped<1, 4, 1, 1, true, __nv_bfloat16>(grid_f, stream, "moe_gate_up_grouped", hh, K, zero, rp, top, wgu,
-                                                        gu_group, a, F, zero, F, K, te, t0, tr, nt, 0, kind, limit);
+                                                        gu_group, a, F, zero, F, K, te, t0, tr, nt, 0, kind, limit, packed);
   if (rc != GB_OK) return rc;
   const __nv_bfloat16* ac = a;
   if (tall)
     rc = launch_grouped<4, 2, 2, 2, false, float>(grid_n, stream, "moe_down_grouped", ac, F, zero, none, 1, wd, d_group, y, N,
-                                                 zero, N, F, te, t0, tr, nt, 0, 0, 0.f);
+                                                 zero, N, F, te, t0, tr, nt, 0, 0, 0.f, 0);
   else
     rc = launch_grouped<1, 4, 1, 1, false, float>(grid_n, stream, "moe_down_grouped", ac, F, zero, none, 1, wd, d_group, y, N,
-                                                 zero, N, F, te, t0, tr, nt, 0, 0, 0.f);
+                                                 zero, N, F, te, t0, tr, nt, 0, 0, 0.f, 0);
   if (rc != GB_OK) return rc;
+  moe_combine_kernel<<<T, 256, 0, stream>>>(y, pair_row, weights, x, top, N, alpha);
+  return gb::check_launch("moe_combine");
+}
+
+namespace {
+
+constexpr int BLOCK_ROWS = 128;       // rows of a block of the tcgen05 grouped product: every block of one expert
+
+// One block. Pair p = t * top + j goes to expert ids[p]; an expert's rows start at a multiple of
+// BLOCK_ROWS. Out: pair_row[R] (pair -> row of the padded order) and, per block of rows, the first
+// weight row of its expert in the stacked gate/up and down weights (blocks beyond the used ones: 0).
+__global__ void __launch_bounds__(SORT_THREADS)
+moe_sort_padded_kernel(const int32_t* __restrict__ ids, int R, int E, int gu_rows, int dn_rows, int blocks,
+                       int32_t* __restrict__ pair_row, int32_t* __restrict__ block_w_gu, int32_t* __restrict__ block_w_dn) {
+  extern __shared__ int32_t sm[];
+  int32_t* counts = sm;
+  int32_t* cursor = sm + E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < R; p += blockDim.x) {
+    const int e = ids[p];
+    if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int blk = 0;
+    for (int e = 0; e < E; ++e) {
+      cursor[e] = blk * BLOCK_ROWS;
+      for (int c = counts[e]; c > 0 && blk < blocks; c -= BLOCK_ROWS, ++blk) {
+        block_w_gu[blk] = e * gu_rows;
+        block_w_dn[blk] = e * dn_rows;
+      }
+    }
+    for (; blk < blocks; ++blk) block_w_gu[blk] = block_w_dn[blk] = 0;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < R; p += blockDim.x) {
+    const int e = ids[p];
+    pair_row[p] = (e >= 0 && e < E) ? atomicAdd(&cursor[e], 1) : -1;
+  }
+}
+
+// a[pair_row[p]] = h[p / top] (rows of K bfloat16, K a multiple of 8), one block per pair
+__global__ void __launch_bounds__(128)
+moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ h, const int32_t* __restrict__ pair_row, int top, int K,
+                       __nv_bfloat16* __restrict__ a) {
+  const int p = blockIdx.x, row = pair_row[p];
+  if (row < 0) return;
+  const uint4* src = reinterpret_cast<const uint4*>(h + (size_t)(p / top) * K);
+  uint4* dst = reinterpret_cast<uint4*>(a + (size_t)row * K);
+  for (int c = threadIdx.x; c < K / 8; c += blockDim.x) dst[c] = src[c];
+}
+
+}  // namespace
+
+// Rows of the padded order for R pairs over E experts (a multiple of 128), and its blocks.
+GB_EXPORT long long gb_moe_padded_rows(long long R, int E) { return ((R + BLOCK_ROWS - 1) / BLOCK_ROWS + E) * BLOCK_ROWS; }
+
+// For the tcgen05 grouped products: pairs sorted by expert into blocks of 128 rows, the tokens' rows
+// gathered (padding rows zero). index: pair_row [R], then block_w_gu and block_w_dn [rows / 128 each].
+GB_EXPORT int gb_moe_padded_prepare(const void* h, const int32_t* ids, int T, int top, int E, int K, int gu_rows,
+                                    int dn_rows, int32_t* index, void* a_sorted, cudaStream_t stream) {
+  if (T <= 0) return GB_OK;
+  if (K % 8 || E < 1 || (size_t)E * 2 * sizeof(int32_t) > 40 * 1024)
+    return gb::fail(GB_UNSUPPORTED, "moe_padded_prepare: width %d, %d experts", K, E);
+  const long long R = (long long)T * top, rows = gb_moe_padded_rows(R, E);
+  const int blocks = (int)(rows / BLOCK_ROWS);
+  int32_t* pair_row = index;
+  int32_t* block_w_gu = index + R;
+  int32_t* block_w_dn = block_w_gu + blocks;
+  cudaError_t e = cudaMemsetAsync(a_sorted, 0, (size_t)rows * K * sizeof(__nv_bfloat16), stream);
+  if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "moe_padded_prepare: %s", cudaGetErrorString(e));
+  moe_sort_padded_kernel<<<1, SORT_THREADS, (size_t)E * 2 * sizeof(int32_t), stream>>>(ids, (int)R, E, gu_rows, dn_rows, blocks,
+                                                                                      pair_row, block_w_gu, block_w_dn);
+  int rc = gb::check_launch("moe_sort_padded");
+  if (rc != GB_OK) return rc;
+  moe_gather_rows_kernel<<<(unsigned)R, 128, 0, stream>>>((const __nv_bfloat16*)h, pair_row, top, K, (__nv_bfloat16*)a_sorted);
+  return gb::check_launch("moe_gather_rows");
+}
+
+// x[t] += alpha * sum_j weights[t][j] * y[pair_row[t * top + j]], j in the router's order
+GB_EXPORT int gb_moe_combine(const float* y, const int32_t* pair_row, const float* weights, float* x, int T, int top,
+                             int N, float alpha, cudaStream_t stream) {
+  if (T <= 0) return GB_OK;
   moe_combine_kernel<<<T, 256, 0, stream>>>(y, pair_row, weights, x, top, N, alpha);
   return gb::check_launch("moe_combine");
 }
@@ -305,8 +393,8 @@ GB_EXPORT int gb_grouped_gemm(const void* a, int lda, long long a_group, const v
   if (M >= 48)
     return launch_grouped<4, 2, 2, 2, false, __nv_bfloat16>(dim3((N + GN - 1) / GN, (M + TALL - 1) / TALL, groups), stream,
                                                            "grouped_gemm", aa, lda, a_group, none, 1, ww, w_group, oo, ldo,
-                                                           out_group, N, K, none, none, none, none, M, 0, 0.f);
+                                                           out_group, N, K, none, none, none, none, M, 0, 0.f, 0);
   return launch_grouped<1, 4, 1, 1, false, __nv_bfloat16>(dim3((N + GN - 1) / GN, (M + SHORT - 1) / SHORT, groups), stream,
                                                          "grouped_gemm", aa, lda, a_group, none, 1, ww, w_group, oo, ldo,
-                                                         out_group, N, K, none, none, none, none, M, 0, 0.f);
+                                                         out_group, N, K, none, none, none, none, M, 0, 0.f, 0);
 }

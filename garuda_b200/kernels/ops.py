@@ -160,6 +160,8 @@ class CudaOps:
                 fn.restype = c_int
             L.gb_moe_grouped_index_words.argtypes = [c_longlong, c_int]
             L.gb_moe_grouped_index_words.restype = c_longlong
+            L.gb_moe_padded_rows.argtypes = [c_longlong, c_int]
+            L.gb_moe_padded_rows.restype = c_longlong
             self._mixers = L
         return self._mixers
 
@@ -174,7 +176,10 @@ class CudaOps:
                                c_int, c_float, c_void_p],
             "gb_moe_down": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                             c_float, c_void_p],
-            "gb_moe_grouped": [c_void_p] * 6 + [c_int] * 7 + [c_float, c_float] + [c_void_p] * 4,
+            "gb_moe_grouped": [c_void_p] * 6 + [c_int] * 7 + [c_float, c_float, c_int] + [c_void_p] * 4,
+            "gb_moe_padded_prepare": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                      c_void_p],
+            "gb_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
             "gb_grouped_gemm": [c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_longlong,
                                 c_int, c_int, c_int, c_int, c_void_p],
             "gb_latent_query_prepare": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
@@ -591,19 +596,37 @@ class CudaOps:
             act.data_ptr(), _tag(act, "act"), w_down.data_ptr(), _tag(w_down, "w"), ids.data_ptr(),
             weights.data_ptr(), x.data_ptr(), T, top, F, N, float(alpha), self._stream()), "moe_down")
 
+    def pack_expert_gate_up(self, gates, ups):
+        """The experts' gate and up matrices stacked, in the layout ``routed_feed_forward`` wants:
+        ``[E, 2F, K]`` (an expert's gate rows, then its up rows), or, where the tensor-core products
+        take the sizes, every expert packed as ``pack_gate_up`` packs: ``[E, 128 ceil(F / 64), K]``."""
+        F, K = gates[0].shape
+        if self.tc is not None and gates[0].dtype == torch.bfloat16 and K % 8 == 0 and F % 8 == 0 and len(gates) <= 4096:
+            packed = torch.stack([self.pack_gate_up(g, u) for g, u in zip(gates, ups)]).contiguous()
+            packed.gb_group = 64
+            return packed
+        return torch.stack([torch.cat([g, u], dim=0) for g, u in zip(gates, ups)]).contiguous()
+
+    #: (token, choice) pairs from which the routed experts run on the tcgen05 grouped product
+    GROUPED_TC_PAIRS = 1024
+
     def routed_feed_forward(self, ctx, h, w_gate_up, w_down, ids, weights, x, kind: str, limit: float,
                             alpha: float = 1.0):
         """``x[t] += alpha * sum_j weights[t, j] * expert_{ids[t, j]}(h[t])`` with the experts'
-        weights stacked: ``w_gate_up [E, 2F, K]``, ``w_down [E, N, F]``."""
+        weights stacked: ``w_gate_up`` from ``pack_expert_gate_up``, ``w_down [E, N, F]``."""
         T, top = ids.shape
         E, N, F = w_down.shape
         K = h.shape[1]
-        if self.tc is not None and h.dtype == torch.bfloat16 and K % 8 == 0 and F % 8 == 0 and E <= 4096:
+        packed = getattr(w_gate_up, "gb_group", 0) == 64
+        if packed and T * top >= self.GROUPED_TC_PAIRS and self._routed_tcgen05(ctx, h, w_gate_up, w_down, ids, weights,
+                                                                               x, kind, limit, alpha):
+            return
+        if packed:
             # on the tensor cores: pairs sorted by expert on the device, two grouped products, a weighted sum
             self._on_device(h, w_gate_up, w_down, ids, weights, x)
             _need(h.is_contiguous() and w_gate_up.is_contiguous() and w_down.is_contiguous() and ids.is_contiguous()
                   and weights.is_contiguous() and x.is_contiguous() and x.dtype == torch.float32
-                  and tuple(w_gate_up.shape) == (E, 2 * F, K) and x.shape == (T, N) and ids.dtype == torch.int32
+                  and tuple(w_gate_up.shape) == (E, 128 * ((F + 63) // 64), K) and x.shape == (T, N) and ids.dtype == torch.int32
                   and weights.dtype == torch.float32 and w_gate_up.dtype == w_down.dtype == torch.bfloat16,
                   "routed_feed_forward: shapes")
             L = self.mixers
@@ -613,12 +636,44 @@ class CudaOps:
             y = ctx.ws.get("expert_rows", (T * top, N), torch.float32)
             self._check(L, L.gb_moe_grouped(
                 h.data_ptr(), w_gate_up.data_ptr(), w_down.data_ptr(), ids.data_ptr(), weights.data_ptr(), x.data_ptr(),
-                T, top, E, F, K, N, self.GATE_ACTS[kind], float(limit), float(alpha), index.data_ptr(), act.data_ptr(),
+                T, top, E, F, K, N, self.GATE_ACTS[kind], float(limit), float(alpha), 1, index.data_ptr(), act.data_ptr(),
                 y.data_ptr(), self._stream()), "moe_grouped", 4)
             return
         act = ctx.ws.get("expert_act", (T, top, F), h.dtype)
         self.moe_gate_up(h, w_gate_up, ids, act, kind, limit)
         self.moe_down(act, w_down, ids, weights, x, alpha)
+
+    def _routed_tcgen05(self, ctx, h, w_gate_up, w_down, ids, weights, x, kind, limit, alpha) -> bool:
+        """Many pairs: sorted by expert into blocks of 128 rows (padding rows zero), then the two
+        products on the tcgen05 many-token kernel with each block's expert read from a list."""
+        T, top = ids.shape
+        E, N, F = w_down.shape
+        K = h.shape[1]
+        L, tc = self.mixers, self.tc
+        rows = int(L.gb_moe_padded_rows(T * top, E))
+        blocks = rows // 128
+        gu_rows = w_gate_up.shape[1]
+        a = ctx.ws.get("expert_in", (rows, K), torch.bfloat16)
+        act = ctx.ws.get("expert_act_padded", (rows, F), torch.bfloat16)
+        if not (tc.lib.gb_gemm_tc_supported(a.data_ptr(), w_gate_up.data_ptr(), rows, F, K)
+                and tc.lib.gb_gemm_tc_supported(act.data_ptr(), w_down.data_ptr(), rows, N, F)):
+            return False
+        self._on_device(h, w_gate_up, w_down, ids, weights, x)
+        _need(h.is_contiguous() and w_gate_up.is_contiguous() and w_down.is_contiguous() and ids.is_contiguous()
+              and weights.is_contiguous() and x.is_contiguous() and x.dtype == torch.float32 and x.shape == (T, N)
+              and ids.dtype == torch.int32 and weights.dtype == torch.float32
+              and h.dtype == w_gate_up.dtype == w_down.dtype == torch.bfloat16, "routed_feed_forward: shapes")
+        index = ctx.ws.get("expert_index_padded", (T * top + 2 * blocks,), torch.int32)
+        y = ctx.ws.get("expert_rows_padded", (rows, N), torch.float32)
+        self._check(L, L.gb_moe_padded_prepare(h.data_ptr(), ids.data_ptr(), T, top, E, K, gu_rows, N, index.data_ptr(),
+                                               a.data_ptr(), self._stream()), "moe_padded_prepare", 2)
+        block_gu = index.data_ptr() + 4 * T * top
+        block_dn = block_gu + 4 * blocks
+        tc.grouped(a, w_gate_up, act, F, E, block_gu, 2, gate_act=self.GATE_ACTS[kind], gate_limit=limit)
+        tc.grouped(act, w_down, y, N, E, block_dn, 0)
+        self._check(L, L.gb_moe_combine(y.data_ptr(), index.data_ptr(), weights.data_ptr(), x.data_ptr(), T, top, N,
+                                        float(alpha), self._stream()), "moe_combine")
+        return True
 
     # ------------------------------------------------------------------ attention over a cached latent
     def latent_append(self, src, norm_w, eps, rank, rot, rotary, positions, token_req, block_table, pool, page_size):

@@ -33,6 +33,9 @@ class TensorCoreKernels:
         L.gb_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                  ctypes.POINTER(NormFold), c_float, c_int, c_float, c_void_p]
         L.gb_gemm_tc.restype = c_int
+        L.gb_gemm_tc_grouped.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int,
+                                         c_float, c_int, c_float, c_void_p]
+        L.gb_gemm_tc_grouped.restype = c_int
         L.gb_gemm_tc_norm_tiles.argtypes = [c_int, c_int]
         L.gb_gemm_tc_norm_tiles.restype = c_int
         L.gb_gemm_tc_supported.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int]
@@ -128,6 +131,17 @@ class TensorCoreKernels:
                                    float(gate_limit), self.ops._stream())
         self.ops._check(self.lib, code, "gemm_tc")
         return True
+
+    def grouped(self, a, w, out, n_out, groups, block_w_row, epi, gate_act: int = 0, gate_limit: float = 0.0) -> None:
+        """A grouped product: ``a [rows, K]`` sorted by group in blocks of 128 rows, ``w [groups, *, K]``
+        the groups' weights, ``block_w_row``: device address of the int32 list that gives every block
+        the first weight row of its group. ``epi`` 0: ``out = a w^T``; 2: the gated epilogue."""
+        rows, K = a.shape
+        self._stream(w)
+        code = self.lib.gb_gemm_tc_grouped(a.data_ptr(), w.data_ptr(), out.data_ptr(), rows, int(n_out), K, int(groups),
+                                           block_w_row, 0 if out.dtype == torch.float32 else 1, int(epi), 1.0,
+                                           int(gate_act), float(gate_limit), self.ops._stream())
+        self.ops._check(self.lib, code, "gemm_tc_grouped")
 
     def linear(self, a, w, out, accumulate, emit=None, alpha: float = 1.0) -> bool:
         """``emit``: a ``PendingNorm`` whose values and sums this accumulating product fills."""

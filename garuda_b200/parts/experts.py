@@ -55,9 +55,9 @@ class RoutedExperts(FeedForward):
         self.w_router = tensors["router"].contiguous()
         self.b_router = tensors["router.b"].float().contiguous() if self.router_bias else None
         E = self.experts
-        # [E, 2 inner, width]: an expert's gate rows, then its up rows; [E, width, inner]
-        self.w_gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0)
-                                      for e in range(E)]).contiguous()
+        # the experts' gate and up rows stacked in the kernels' layout; [E, width, inner]
+        self.w_gate_up = ops.pack_expert_gate_up([tensors[f"e{e}.gate"] for e in range(E)],
+                                                 [tensors[f"e{e}.up"] for e in range(E)])
         self.w_down = torch.stack([tensors[f"e{e}.down"] for e in range(E)]).contiguous()
         if self.shared_inner:
             self.w_shared_gate_up = ops.pack_gate_up(tensors["shared.gate"], tensors["shared.up"])

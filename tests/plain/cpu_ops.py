@@ -214,6 +214,9 @@ class CpuOps:
                 total += weights[t, j] * (w_down[int(ids[t, j])].float() @ act[t, j].float())
             x[t] += alpha * total
 
+    def pack_expert_gate_up(self, gates, ups):
+        return torch.stack([torch.cat([g, u], 0) for g, u in zip(gates, ups)]).contiguous()
+
     def routed_feed_forward(self, ctx, h, w_gate_up, w_down, ids, weights, x, kind, limit, alpha=1.0):
         T, top = ids.shape
         act = torch.zeros(T, top, w_down.shape[2], dtype=h.dtype)

@@ -113,7 +113,8 @@ def test_gate_up_product_with_the_activation_in_its_epilogue(both, kind, limit, 
 
 
 @pytest.mark.parametrize("T,E,top,K,F", [(1, 4, 4, 40, 16), (37, 16, 4, 192, 24), (130, 33, 1, 72, 50), (9, 64, 8, 256, 64),
-                                         (300, 5, 2, 136, 72), (700, 16, 4, 192, 64), (8, 32, 4, 512, 200)])
+                                         (300, 5, 2, 136, 72), (700, 16, 4, 192, 64), (8, 32, 4, 512, 200), (1100, 7, 3, 256, 136),
+                                         (2048, 16, 4, 512, 320)])
 def test_router_and_routed_experts(both, T, E, top, K, F):
     ops, cpu, dt = both
     h, wr, br = rnd(T, K, dtype=dt), rnd(E, K, dtype=dt, scale=0.5, seed=1), rnd(E, seed=2)
@@ -124,10 +125,14 @@ def test_router_and_routed_experts(both, T, E, top, K, F):
     assert torch.equal(ids.cpu(), ids_c)
     close(wt, wt_c, torch.float32, "router weights")
     assert torch.allclose(wt.sum(-1).cpu(), torch.ones(T), atol=1e-5)
-    wgu, wd, x = rnd(E, 2 * F, K, dtype=dt, scale=0.3, seed=3), rnd(E, K, F, dtype=dt, scale=0.3, seed=4), rnd(T, K, seed=5)
+    gates = [rnd(F, K, dtype=dt, scale=0.3, seed=30 + e) for e in range(E)]
+    ups = [rnd(F, K, dtype=dt, scale=0.3, seed=300 + e) for e in range(E)]
+    wd, x = rnd(E, K, F, dtype=dt, scale=0.3, seed=4), rnd(T, K, seed=5)
     g, c = x.clone().cuda(), x.clone()
-    ops.routed_feed_forward(_Ctx(), h.cuda(), wgu.cuda(), wd.cuda(), ids, wt, g, "clamped_swish", 1.5, 0.3)
-    cpu.routed_feed_forward(None, h, wgu, wd, ids_c, wt_c, c, "clamped_swish", 1.5, 0.3)
+    # in the layout the kernels want: packed per expert where the tensor-core products take the sizes
+    wgu = ops.pack_expert_gate_up([t.cuda() for t in gates], [t.cuda() for t in ups])
+    ops.routed_feed_forward(_Ctx(), h.cuda(), wgu, wd.cuda(), ids, wt, g, "clamped_swish", 1.5, 0.3)
+    cpu.routed_feed_forward(None, h, cpu.pack_expert_gate_up(gates, ups), wd, ids_c, wt_c, c, "clamped_swish", 1.5, 0.3)
     close(g, c, dt, "routed experts")
 
 
