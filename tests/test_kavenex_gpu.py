@@ -46,7 +46,7 @@ def close(got, want, dt, what):
     assert torch.isfinite(got).all() and err <= tol, f"{what}: {err:.2e}"
 
 
-@pytest.mark.parametrize("T,d", [(1, 40), (37, 192), (5, 1030), (3, 4096), (2, 6000), (4, 2052)])
+@pytest.mark.parametrize("T,d", [(1, 40), (37, 200), (5, 1030), (3, 4096), (2, 6000), (4, 2052)])
 def test_layer_norm_rms_add_and_residual_forms(both, T, d):
     ops, cpu, dt = both
     x, y, w, b = rnd(T, d), rnd(T, d, seed=1), rnd(d, dtype=dt, seed=2), rnd(d, dtype=dt, seed=3)
@@ -91,7 +91,7 @@ def test_gated_activations_and_the_token_gate(both, kind, limit):
     close(out, ref, dt, "gelu_gather_mul")
 
 
-@pytest.mark.parametrize("M,N,K", [(3, 48, 40), (70, 192, 128), (300, 72, 200)])
+@pytest.mark.parametrize("M,N,K", [(3, 48, 40), (70, 160, 128), (300, 72, 200)])
 def test_product_into_the_residual_with_a_multiplier(both, M, N, K):
     ops, cpu, dt = both
     a, w, x = rnd(M, K, dtype=dt), rnd(N, K, dtype=dt, scale=0.1, seed=1), rnd(M, N, seed=2)
@@ -102,7 +102,7 @@ def test_product_into_the_residual_with_a_multiplier(both, M, N, K):
 
 
 @pytest.mark.parametrize("kind,limit", [("gelu_tanh", 0.0), ("clamped_swish", 1.0), ("silu", 0.0)])
-@pytest.mark.parametrize("M,F,K", [(1, 64, 128), (9, 320, 192), (64, 96, 64), (200, 200, 128), (700, 512, 256), (33, 50, 44)])
+@pytest.mark.parametrize("M,F,K", [(1, 64, 128), (9, 328, 184), (64, 96, 64), (200, 200, 128), (700, 512, 256), (33, 50, 44)])
 def test_gate_up_product_with_the_activation_in_its_epilogue(both, kind, limit, M, F, K):
     ops, cpu, dt = both
     h, g, u = rnd(M, K, dtype=dt), rnd(F, K, dtype=dt, scale=0.25, seed=1), rnd(F, K, dtype=dt, scale=0.25, seed=2)
@@ -112,8 +112,8 @@ def test_gate_up_product_with_the_activation_in_its_epilogue(both, kind, limit, 
     close(act, ref, dt, f"gate/up with {kind}")
 
 
-@pytest.mark.parametrize("T,E,top,K,F", [(1, 4, 4, 40, 16), (37, 16, 4, 192, 24), (130, 33, 1, 72, 50), (9, 64, 8, 256, 64),
-                                         (300, 5, 2, 136, 72), (700, 16, 4, 192, 64), (8, 32, 4, 512, 200), (1100, 7, 3, 256, 136),
+@pytest.mark.parametrize("T,E,top,K,F", [(1, 4, 4, 40, 16), (37, 12, 3, 176, 24), (130, 33, 1, 72, 50), (9, 64, 8, 256, 64),
+                                         (300, 5, 2, 136, 72), (700, 12, 4, 160, 72), (8, 32, 4, 512, 200), (1100, 7, 3, 256, 136),
                                          (2048, 16, 4, 512, 320)])
 def test_router_and_routed_experts(both, T, E, top, K, F):
     ops, cpu, dt = both
@@ -146,7 +146,7 @@ def test_router_ties_go_to_the_lower_index(both):
     assert ids.cpu().tolist() == [[1, 4, 0], [1, 4, 0]]
 
 
-@pytest.mark.parametrize("rank,rot,dims,H,dn,dv", [(24, 8, 6, 3, 10, 12), (96, 32, 32, 4, 32, 32), (200, 40, 40, 2, 24, 56),
+@pytest.mark.parametrize("rank,rot,dims,H,dn,dv", [(24, 8, 6, 3, 10, 12), (80, 16, 16, 4, 24, 40), (200, 40, 40, 2, 24, 56),
                                                    (512, 64, 64, 2, 64, 64)])
 def test_latent_cache_rows_head_products_and_attention_over_them(both, rank, rot, dims, H, dn, dv):
     from garuda_b200.parts.rotary import RotaryParams
@@ -187,7 +187,7 @@ def test_latent_cache_rows_head_products_and_attention_over_them(both, rank, rot
     close(o, o_c, dt, "values out of the latent")
 
 
-@pytest.mark.parametrize("T,H,dn,rot,dims,rank", [(5, 3, 10, 8, 6, 24), (300, 4, 32, 32, 32, 96), (70, 16, 64, 64, 64, 512)])
+@pytest.mark.parametrize("T,H,dn,rot,dims,rank", [(5, 3, 10, 8, 6, 24), (300, 4, 24, 16, 16, 80), (70, 16, 64, 64, 64, 512)])
 def test_query_rows_prepared_and_mapped_into_the_latent(both, T, H, dn, rot, dims, rank):
     from garuda_b200.parts.rotary import RotaryParams
     ops, cpu, dt = both
