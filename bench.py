@@ -5,6 +5,9 @@
 
     python bench.py --shape tinyllama|llama2-7b|llama3-8b [--layers L]
 
+    python bench.py --design kavenex [--size 2k,4k]     (a JSON line of its own: the second architecture
+                                                         beside Llama at equal sizes, kernel beside like kernel)
+
 A step is one decode step: every live request advances by one token. The default
 run has the layer sizes of TinyLlama-1.1B with random weights, 8 requests and a
 context of 2,048 tokens; ``--shape`` chooses another of the reference's published
