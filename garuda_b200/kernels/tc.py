@@ -297,12 +297,12 @@ class TensorCoreKernels:
     @staticmethod
     def latent_plan(num_requests: int, heads: int, max_q_len: int, max_kv_len: int) -> int:
         """CTAs that share a query tile's keys: one when the tiles alone fill the GPU, else enough for
-        about two CTAs an SM, each with at least 256 keys, at most 16 (every split writes and the
+        about two CTAs an SM, each with at least 128 keys, at most 16 (every split writes and the
         merge reads a 32-bit partial row per query row)."""
         tiles = -(-max_q_len * heads // 64) * max(num_requests, 1)
         if tiles >= 120:
             return 1
-        return max(1, min(296 // tiles, -(-max_kv_len // 256), 16))
+        return max(1, min(296 // tiles, -(-max_kv_len // 128), 16))
 
     def latent_attention(self, q, pool, out, block_table, cu_q, kv_lens, rank, scale, page_size, num_requests,
                          max_q_len, max_kv_len, ws=None) -> bool:
