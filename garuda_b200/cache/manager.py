@@ -44,7 +44,7 @@ class PagedCache:
             raise ValueError("the cache needs num_pages or max_tokens")
         self.groups = model.cache_groups
         self.manager = host.CacheManager(
-            [host.GroupConfig(pages, g.need.window or 0) for g in self.groups],
+            [host.GroupConfig(pages, g.need.window or 0, getattr(g.need, "keep_first", 0) or 0) for g in self.groups],
             ps, config.max_requests, config.max_positions)
         self.page_size = ps
         self.table_width = self.manager.max_pages_per_request
@@ -61,9 +61,10 @@ class PagedCache:
                     self.v_pools.append(None)
             else:
                 shape = (len(g.calls), pages, g.need.kv_heads, ps, g.need.head_dim)
+                v_shape = shape[:-1] + (g.need.value_dim or g.need.head_dim,)
                 if allocate:
                     self.k_pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
-                    self.v_pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
+                    self.v_pools.append(torch.zeros(v_shape, dtype=dtype, device=self.device))
             for j, call in enumerate(g.calls):
                 self.call_group[call] = (gi, j)
         self.states: Dict[int, torch.Tensor] = {}
@@ -95,7 +96,8 @@ class PagedCache:
     def bytes_per_position(self) -> int:
         item = self.dtype.itemsize
         return sum(len(g.calls) * (g.need.width if isinstance(g.need, PagedLatent)
-                                   else 2 * g.need.kv_heads * g.need.head_dim) * item for g in self.groups)
+                                   else g.need.kv_heads * (g.need.head_dim + (g.need.value_dim or g.need.head_dim)))
+                   * item for g in self.groups)
 
     # ---- views for a step ------------------------------------------------------
     def layer_caches(self, block_tables: Sequence[torch.Tensor]) -> List[Optional[LayerCache]]:

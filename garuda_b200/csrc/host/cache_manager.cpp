@@ -18,6 +18,7 @@ CacheManager::CacheManager(std::vector<GroupConfig> groups, int page_size, int m
   for (const auto& g : groups_) {
     if (g.num_pages < 0) throw CacheError("a group cannot have a negative number of pages");
     if (g.window < 0) throw CacheError("a window cannot be negative");
+    if (g.keep_first < 0) throw CacheError("the number of kept first positions cannot be negative");
     Pool pool;
     pool.free.reserve(g.num_pages);
     // Highest id at the bottom, so that page 0 is handed out first.
@@ -122,7 +123,7 @@ void CacheManager::commit(int64_t request, int new_len) {
   for (size_t g = 0; g < groups_.size(); ++g) {
     if (groups_[g].window <= 0) continue;
     const int first = first_live_page(static_cast<int>(g), r.len);
-    for (int p = 0; p < first && p < max_pages_; ++p) {
+    for (int p = kept_pages(static_cast<int>(g)); p < first && p < max_pages_; ++p) {
       if (r.tables[g][p] >= 0) {
         pools_[g].free.push_back(r.tables[g][p]);
         r.tables[g][p] = -1;

@@ -34,6 +34,7 @@ struct OutOfPages : CacheError {
 struct GroupConfig {
   int num_pages = 0;   // pages in this group's pool
   int window = 0;      // positions a query looks back over, itself included; 0: everything
+  int keep_first = 0;  // with a window: the first positions of a request that every query still reads
 };
 
 class CacheManager {
@@ -98,6 +99,10 @@ class CacheManager {
   const Request& get(int64_t request) const;
   Request& get(int64_t request);
   int first_live_page(int group, int len) const { return first_live_position(group, len) / page_size_; }
+  // Pages that hold one of a windowed group's kept first positions stay with the request to its end.
+  int kept_pages(int group) const {
+    return groups_[group].window > 0 ? (groups_[group].keep_first + page_size_ - 1) / page_size_ : 0;
+  }
 
   std::vector<GroupConfig> groups_;
   int page_size_, max_requests_, max_positions_, max_pages_;

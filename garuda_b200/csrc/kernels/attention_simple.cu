@@ -9,6 +9,11 @@
 // sum of p_j V_j in key order. Keys are walked 32 at a time from `start`, with
 // a running maximum and sum, so the result for a token does not depend on what
 // else is in the batch or on how its prompt was cut.
+//
+// Options that other designs use, each off at its neutral value: `softcap` c > 0 replaces a score
+// by c tanh(s / c) (after the scale); `keep_first` n > 0 lets a windowed query also read the first
+// n positions of its request (at their true positions); `sink` adds one to the softmax's
+// denominator, an entry of score zero that carries no value: p_j = exp(s_j) / (1 + sum exp(s_k)).
 #include "common.cuh"
 
 namespace {
@@ -24,7 +29,8 @@ attention_simple_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, c
                         const int32_t* __restrict__ block_table, int table_width,
                         const int32_t* __restrict__ cu_q, const int32_t* __restrict__ kv_lens,
                         const int32_t* __restrict__ token_req, T* __restrict__ out, int Hq, int Hkv, int hd,
-                        int v_hd, int vd, float scale, int window, int page_size) {
+                        int v_hd, int vd, float scale, int window, int page_size, float softcap, int keep_first,
+                        int sink) {
   __shared__ float q_s[WARPS][MAX_HD];
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -47,9 +53,16 @@ attention_simple_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, c
   for (int i = 0; i < MAX_HD / 32; ++i) acc[i] = 0.f;
   float m = -INFINITY, l = 0.f;
 
-  for (int base = start; base <= pos; base += 32) {
+  // two stretches of keys: the kept first positions below the window, then the window
+  const int kept = start > 0 ? min(keep_first, start) : 0;
+  const int n_blocks_kept = (kept + 31) / 32;
+  const int n_blocks = n_blocks_kept + (pos - start + 32) / 32;
+  for (int blk = 0; blk < n_blocks; ++blk) {
+    const bool in_kept = blk < n_blocks_kept;
+    const int base = in_kept ? blk * 32 : start + (blk - n_blocks_kept) * 32;
+    const int last = in_kept ? kept - 1 : pos;
     const int j = base + lane;
-    const bool valid = j <= pos;
+    const bool valid = j <= last;
     long long row = -1;  // row of this lane's key in the pool, in units of hd elements
     if (valid) {
       const int page = table[j / page_size];
@@ -61,15 +74,17 @@ attention_simple_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, c
       float dot = 0.f;
       for (int c = 0; c < hd; ++c) dot = fmaf(q_s[warp][c], gb::to_float<T>(kr[c]), dot);
       s = dot * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
     }
     const float m_new = fmaxf(m, gb::warp_max(s));
+    if (m_new == -INFINITY) continue;          // a block without a single stored key
     const float p = row >= 0 ? expf(s - m_new) : 0.f;
     const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
     l = l * corr + gb::warp_sum(p);
     m = m_new;
 #pragma unroll
     for (int i = 0; i < MAX_HD / 32; ++i) acc[i] *= corr;
-    const int n_here = min(32, pos - base + 1);
+    const int n_here = min(32, last - base + 1);
     for (int jj = 0; jj < n_here; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, p, jj);
       const long long rj = __shfl_sync(0xffffffffu, row, jj);
@@ -82,6 +97,7 @@ attention_simple_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, c
       }
     }
   }
+  if (sink && m != -INFINITY) l += expf(-m);
   const float inv = l > 0.f ? 1.0f / l : 0.f;
   T* o = out + ((size_t)t * Hq + h) * vd;
 #pragma unroll
@@ -99,7 +115,7 @@ GB_EXPORT int gb_attention_simple(const void* q, const void* k_pool, const void*
                                   const int32_t* block_table, int table_width, const int32_t* cu_q,
                                   const int32_t* kv_lens, const int32_t* token_req, void* out, int T,
                                   int Hq, int Hkv, int hd, int v_hd, int vd, float scale, int window,
-                                  int page_size, cudaStream_t stream) {
+                                  int page_size, float softcap, int keep_first, int sink, cudaStream_t stream) {
   if (T <= 0) return GB_OK;
   constexpr int WIDEST = 1024;
   if (hd > WIDEST || hd < 1)
@@ -112,11 +128,11 @@ GB_EXPORT int gb_attention_simple(const void* q, const void* k_pool, const void*
     if (hd <= 256 && vd <= 256)
       attention_simple_kernel<TT, 256><<<grid, WARPS * 32, 0, stream>>>(
           (const TT*)q, (const TT*)k_pool, (const TT*)v_pool, block_table, table_width, cu_q, kv_lens,
-          token_req, (TT*)out, Hq, Hkv, hd, v_hd, vd, scale, window, page_size);
+          token_req, (TT*)out, Hq, Hkv, hd, v_hd, vd, scale, window, page_size, softcap, keep_first, sink);
     else
       attention_simple_kernel<TT, WIDEST><<<grid, WARPS * 32, 0, stream>>>(
           (const TT*)q, (const TT*)k_pool, (const TT*)v_pool, block_table, table_width, cu_q, kv_lens,
-          token_req, (TT*)out, Hq, Hkv, hd, v_hd, vd, scale, window, page_size);
+          token_req, (TT*)out, Hq, Hkv, hd, v_hd, vd, scale, window, page_size, softcap, keep_first, sink);
     return gb::check_launch("attention_simple");
   });
 }

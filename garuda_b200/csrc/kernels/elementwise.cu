@@ -13,18 +13,30 @@ namespace {
 // ---------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int32_t* __restrict__ ids,
-                                 float* __restrict__ out, int d, int vocab, float scale) {
+                                 float* __restrict__ out, int d, int vocab, float scale, int copies) {
   gb::pdl_launch_dependents();
   gb::pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
-  float* o = out + (size_t)t * d;
+  float* o = out + (size_t)t * d * copies;       // a token's row `copies` times in a row (a residual of several streams)
   if (id < 0 || id >= vocab) {  // refused on the host before any launch; never read out of range
-    for (int c = threadIdx.x; c < d; c += blockDim.x) o[c] = 0.f;
+    for (int c = threadIdx.x; c < d * copies; c += blockDim.x) o[c] = 0.f;
     return;
   }
   const T* row = table + (size_t)id * d;
-  for (int c = threadIdx.x; c < d; c += blockDim.x) o[c] = gb::to_float<T>(row[c]) * scale;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    const float v = gb::to_float<T>(row[c]) * scale;
+    for (int k = 0; k < copies; ++k) o[(size_t)k * d + c] = v;
+  }
+}
+
+// logits <- logits * scale, then (cap > 0) cap * tanh(logits / cap); in place, 32-bit
+__global__ void scale_softcap_kernel(float* __restrict__ x, long long n, float scale, float cap) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float v = x[i] * scale;
+  if (cap > 0.f) v = cap * tanhf(v / cap);
+  x[i] = v;
 }
 
 // ------------------------------------------------------------------ rmsnorm
@@ -400,13 +412,26 @@ int grid_for(size_t n, int block) {
 }  // namespace
 
 // out[t] = table[ids[t]] * scale (a model without an embedding multiplier passes 1)
-GB_EXPORT int gb_embedding(const void* table, int table_dtype, const int32_t* ids, float* out, int T,
-                           int d, int vocab, float scale, cudaStream_t stream) {
+// out [T, copies, d]: every token's row, scaled, `copies` times
+GB_EXPORT int gb_embedding_copies(const void* table, int table_dtype, const int32_t* ids, float* out, int T,
+                                  int d, int vocab, float scale, int copies, cudaStream_t stream) {
   if (T <= 0) return GB_OK;
+  if (copies < 1) return gb::fail(GB_BAD_ARGUMENT, "embedding: %d copies", copies);
   return GB_DISPATCH_DTYPE(table_dtype, TT, [&]() -> int {
     return gb::check_pdl_launch(gb::launch_pdl(embedding_kernel<TT>, dim3(T), dim3(256), 0, stream, dim3(1, 1, 1),
-                                               (const TT*)table, ids, out, d, vocab, scale), "embedding");
+                                               (const TT*)table, ids, out, d, vocab, scale, copies), "embedding");
   });
+}
+
+GB_EXPORT int gb_embedding(const void* table, int table_dtype, const int32_t* ids, float* out, int T,
+                           int d, int vocab, float scale, cudaStream_t stream) {
+  return gb_embedding_copies(table, table_dtype, ids, out, T, d, vocab, scale, 1, stream);
+}
+
+GB_EXPORT int gb_scale_softcap(float* x, long long n, float scale, float cap, cudaStream_t stream) {
+  if (n <= 0) return GB_OK;
+  scale_softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, n, scale, cap);
+  return gb::check_launch("scale_softcap");
 }
 
 GB_EXPORT int gb_rmsnorm(const float* x, const void* w, int w_dtype, float eps, void* out, int out_dtype,

@@ -13,11 +13,12 @@ constexpr int MAX_TOP = 32;
 
 // One block per token: its warps share out the experts (z_e = h . W[e] + b[e] in 32-bit, the bias
 // 32-bit, each logit one warp's sum in a fixed order), then warp 0 picks the `top` largest in
-// descending order (the lower index first among equals); weights = softmax over the chosen logits.
+// descending order (the lower index first among equals); weights = softmax over the chosen logits
+// (mode 0), or each chosen expert's own sigmoid(z_e), not renormalized (mode 1).
 template <typename HT, typename WT>
 __global__ void __launch_bounds__(256)
 route_topk_kernel(const HT* __restrict__ h, const WT* __restrict__ w, const float* __restrict__ bias, int T, int E,
-                  int K, int top, int32_t* __restrict__ ids, float* __restrict__ weights) {
+                  int K, int top, int mode, int32_t* __restrict__ ids, float* __restrict__ weights) {
   gb::pdl_launch_dependents();
   gb::pdl_wait();
   extern __shared__ float sm[];        // z[E], then h[K]
@@ -56,7 +57,9 @@ route_topk_kernel(const HT* __restrict__ h, const WT* __restrict__ w, const floa
     }
     __syncwarp();
   }
-  if (lane == 0) {
+  if (lane == 0 && mode == 1) {
+    for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] = 1.0f / (1.0f + expf(-chosen[j]));
+  } else if (lane == 0) {
     const float largest = chosen[0];
     float sum = 0.f;
     for (int j = 0; j < top; ++j) {
@@ -79,15 +82,19 @@ __device__ __forceinline__ float gate_act(int kind, float limit, float g, float 
 
 // grid (T, top). act[(t * top + j)][f] = act(gate_e[f] . h_t, up_e[f] . h_t), e = ids[t][j]; the
 // expert's weights are [2F, K]: F gate rows, then F up rows. A warp per feature, lanes over k.
+// in_scale [T, top] (or null): the pair's factor on the expert's input, expert(s h): both products
+// are linear in h, so they are multiplied by s before the activation.
 template <typename HT, typename WT, typename OT>
 __global__ void __launch_bounds__(128)
 moe_gate_up_kernel(const HT* __restrict__ h, const WT* __restrict__ w, const int32_t* __restrict__ ids,
-                   OT* __restrict__ act, int top, int F, int K, int kind, float limit) {
+                   OT* __restrict__ act, int top, int F, int K, int kind, float limit,
+                   const float* __restrict__ in_scale) {
   extern __shared__ float h_s[];
   const int t = blockIdx.x, j = blockIdx.y;
   for (int k = threadIdx.x; k < K; k += blockDim.x) h_s[k] = gb::to_float<HT>(h[(size_t)t * K + k]);
   __syncthreads();
   const int e = ids[(size_t)t * top + j];
+  const float s_in = in_scale ? in_scale[(size_t)t * top + j] : 1.0f;
   const WT* we = w + (size_t)e * 2 * F * K;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int f = warp; f < F; f += 4) {
@@ -98,13 +105,13 @@ moe_gate_up_kernel(const HT* __restrict__ h, const WT* __restrict__ w, const int
       g = fmaf(h_s[k], gb::to_float<WT>(gr[k]), g);
       u = fmaf(h_s[k], gb::to_float<WT>(ur[k]), u);
     }
-    g = gb::warp_sum(g);
-    u = gb::warp_sum(u);
+    g = gb::warp_sum(g) * s_in;
+    u = gb::warp_sum(u) * s_in;
     if (lane == 0) act[((size_t)t * top + j) * F + f] = gb::from_float<OT>(gate_act(kind, limit, g, u));
   }
 }
 
-// One block per token. x[t][n] += alpha * sum_j weights[t][j] * (down_e(j)[n] . act[t][j]).
+// One block per token. x[t][n] += alpha * sum_j weights[t][j] * (down_e(j)[n] . act[t][j]); weights null: all one.
 template <typename AT, typename WT>
 __global__ void __launch_bounds__(256)
 moe_down_kernel(const AT* __restrict__ act, const WT* __restrict__ w, const int32_t* __restrict__ ids,
@@ -121,7 +128,7 @@ moe_down_kernel(const AT* __restrict__ act, const WT* __restrict__ w, const int3
       const WT* wr = w + ((size_t)e * N + n) * F;
       float acc = 0.f;
       for (int f = lane; f < F; f += 32) acc = fmaf(a_s[j * F + f], gb::to_float<WT>(wr[f]), acc);
-      total = fmaf(weights[(size_t)t * top + j], gb::warp_sum(acc), total);
+      total = fmaf(weights ? weights[(size_t)t * top + j] : 1.0f, gb::warp_sum(acc), total);
     }
     if (lane == 0) x[(size_t)t * N + n] = fmaf(alpha, total, x[(size_t)t * N + n]);
   }
@@ -130,8 +137,9 @@ moe_down_kernel(const AT* __restrict__ act, const WT* __restrict__ w, const int3
 }  // namespace
 
 GB_EXPORT int gb_route_topk(const void* h, int h_dtype, const void* w, const float* bias, int w_dtype, int T, int E,
-                            int K, int top, int32_t* ids, float* weights, cudaStream_t stream) {
+                            int K, int top, int mode, int32_t* ids, float* weights, cudaStream_t stream) {
   if (T <= 0) return GB_OK;
+  if (mode != 0 && mode != 1) return gb::fail(GB_BAD_ARGUMENT, "route_topk: mode %d", mode);
   if (E < 1 || E > MAX_EXPERTS || top < 1 || top > MAX_TOP || top > E)
     return gb::fail(GB_UNSUPPORTED, "route_topk: %d of %d experts (at most %d of %d)", top, E, MAX_TOP, MAX_EXPERTS);
   const size_t smem = (size_t)(E + K) * sizeof(float);
@@ -144,7 +152,7 @@ GB_EXPORT int gb_route_topk(const void* h, int h_dtype, const void* w, const flo
       }
       return gb::check_pdl_launch(
           gb::launch_pdl(route_topk_kernel<HT, WT>, dim3(T), dim3(256), smem, stream,
-                         dim3(1, 1, 1), (const HT*)h, (const WT*)w, bias, T, E, K, top, ids, weights),
+                         dim3(1, 1, 1), (const HT*)h, (const WT*)w, bias, T, E, K, top, mode, ids, weights),
           "route_topk");
     });
   });
@@ -152,14 +160,14 @@ GB_EXPORT int gb_route_topk(const void* h, int h_dtype, const void* w, const flo
 
 GB_EXPORT int gb_moe_gate_up(const void* h, int h_dtype, const void* w, int w_dtype, const int32_t* ids, void* act,
                              int act_dtype, int T, int top, int F, int K, int kind, float limit,
-                             cudaStream_t stream) {
+                             const float* in_scale, cudaStream_t stream) {
   if (T <= 0) return GB_OK;
   if ((size_t)K * sizeof(float) > 48 * 1024) return gb::fail(GB_UNSUPPORTED, "moe_gate_up: width %d", K);
   return GB_DISPATCH_DTYPE(h_dtype, HT, [&]() -> int {
     return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
       return GB_DISPATCH_DTYPE(act_dtype, OT, [&]() -> int {
         moe_gate_up_kernel<HT, WT, OT><<<dim3(T, top), 128, (size_t)K * sizeof(float), stream>>>(
-            (const HT*)h, (const WT*)w, ids, (OT*)act, top, F, K, kind, limit);
+            (const HT*)h, (const WT*)w, ids, (OT*)act, top, F, K, kind, limit, in_scale);
         return gb::check_launch("moe_gate_up");
       });
     });

@@ -83,14 +83,17 @@ __device__ __forceinline__ float gate_act(int kind, float limit, float g, float 
 // rows (or the packed layout, see `packed`), and out (bfloat16) is act(gate, up). With a tile list (tile_expert ...) the CTA reads its
 // group and rows from it; without, blockIdx.z is the group and every group has `rows_all` rows.
 // The CTA is WM x WN warps, a warp's tile (MI * 16) x (NP * 16): 128 x 64 for groups of many rows,
-// 16 x 64 for a few rows per group, where a taller tile would be padding.
+// 16 x 64 for a few rows per group, where a taller tile would be padding. GATED with in_scale: the
+// products of row r are multiplied by in_scale[gather[row0 + r]] before the activation (a factor on
+// the expert's input, in which both products are linear).
 template <int WM, int WN, int MI, int NP, bool GATED, typename OT>
 __global__ void __launch_bounds__(WM * WN * 32)
 grouped_gemm_kernel(const __nv_bfloat16* __restrict__ a, int lda, long long a_group, const int32_t* __restrict__ gather,
                     int gather_div, const __nv_bfloat16* __restrict__ w, long long w_group, OT* __restrict__ out, int ldo,
                     long long out_group, int N, int K, const int32_t* __restrict__ tile_expert,
                     const int32_t* __restrict__ tile_row0, const int32_t* __restrict__ tile_rows,
-                    const int32_t* __restrict__ num_tiles, int rows_all, int kind, float limit, int packed) {
+                    const int32_t* __restrict__ num_tiles, int rows_all, int kind, float limit, int packed,
+                    const float* __restrict__ in_scale) {
   constexpr int TM = WM * MI * 16, TN = WN * NP * 16, THREADS = WM * WN * 32;
   constexpr int BROWS = GATED ? 2 * TN : TN;
   constexpr int CH = GK / 8;                       // 16-byte chunks of a tile's row
@@ -98,6 +101,7 @@ grouped_gemm_kernel(const __nv_bfloat16* __restrict__ a, int lda, long long a_gr
   auto a_tile = [&](int stage) { return tiles + (size_t)stage * (TM + BROWS) * GPITCH; };
   auto b_tile = [&](int stage) { return tiles + ((size_t)stage * (TM + BROWS) + TM) * GPITCH; };
   __shared__ int32_t src_row[TM];
+  __shared__ float row_scale[GATED ? TM : 1];
   int e, row0, rows;
   if (tile_expert != nullptr) {
     const int tile = blockIdx.y;
@@ -111,6 +115,9 @@ grouped_gemm_kernel(const __nv_bfloat16* __restrict__ a, int lda, long long a_gr
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   for (int r = tid; r < TM; r += THREADS)
     src_row[r] = r < rows ? (gather ? gather[row0 + r] / gather_div : row0 + r) : -1;
+  if (GATED)
+    for (int r = tid; r < TM; r += THREADS)
+      row_scale[r] = (in_scale != nullptr && gather != nullptr && r < rows) ? in_scale[gather[row0 + r]] : 1.0f;
   __syncthreads();
   const __nv_bfloat16* ae = a + (size_t)e * a_group;
   const __nv_bfloat16* we = w + (size_t)e * w_group;
@@ -198,12 +205,12 @@ grouped_gemm_kernel(const __nv_bfloat16* __restrict__ a, int lda, long long a_gr
         const int n = n0 + wn * NP * 16 + nt * 8 + 2 * tig + (x & 1);
         if (r >= rows || n >= N) continue;
         float v = acc[mi][nt][x];
-        if (GATED) v = gate_act(kind, limit, v, acc_u[GATED ? mi : 0][nt][x]);
+        if (GATED) v = gate_act(kind, limit, v * row_scale[GATED ? r : 0], acc_u[GATED ? mi : 0][nt][x] * row_scale[GATED ? r : 0]);
         oe[(size_t)(row0 + r) * ldo + n] = gb::from_float<OT>(v);
       }
 }
 
-// x[t][n] += alpha * sum_j weights[t][j] * y[pair_row[t * top + j]][n], j in the router's order
+// x[t][n] += alpha * sum_j weights[t][j] * y[pair_row[t * top + j]][n], j in the router's order; weights null: all one
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ pair_row, const float* __restrict__ weights,
                    float* __restrict__ x, int top, int N, float alpha) {
@@ -212,7 +219,7 @@ moe_combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ pair
     float total = 0.f;
     for (int j = 0; j < top; ++j) {
       const int row = pair_row[(size_t)t * top + j];
-      if (row >= 0) total = fmaf(weights[(size_t)t * top + j], y[(size_t)row * N + n], total);
+      if (row >= 0) total = fmaf(weights ? weights[(size_t)t * top + j] : 1.0f, y[(size_t)row * N + n], total);
     }
     x[(size_t)t * N + n] = fmaf(alpha, total, x[(size_t)t * N + n]);
   }
@@ -247,7 +254,7 @@ GB_EXPORT long long gb_moe_grouped_index_words(long long R, int E) {
 // index: gb_moe_grouped_index_words int32; act: [T * top, F] bfloat16; y: [T * top, N] 32-bit.
 GB_EXPORT int gb_moe_grouped(const void* h, const void* w_gate_up, const void* w_down, const int32_t* ids,
                              const float* weights, float* x, int T, int top, int E, int F, int K, int N, int kind,
-                             float limit, float alpha, int packed, int32_t* index, void* act, float* y,
+                             float limit, float alpha, int packed, int scale_input, int32_t* index, void* act, float* y,
                              cudaStream_t stream) {
   if (T <= 0) return GB_OK;
   if (K % 8 || F % 8) return gb::fail(GB_UNSUPPORTED, "moe_grouped: widths %d and %d must be multiples of 8", K, F);
@@ -274,23 +281,26 @@ GB_EXPORT int gb_moe_grouped(const void* h, const void* w_gate_up, const void* w
   const dim3 grid_f((F + GN - 1) / GN, max_tiles), grid_n((N + GN - 1) / GN, max_tiles);
   const int32_t* none = nullptr;
   const int32_t *te = tile_expert, *t0 = tile_row0, *tr = tile_rows, *nt = num_tiles, *rp = row_pair;
+  const float* in_scale = scale_input ? weights : nullptr;       // the weights scale what goes into an expert ...
+  const float* out_weights = scale_input ? nullptr : weights;    // ... or what comes out of it
+  const float* no_scale = nullptr;
   const long long zero = 0, gu_group = (long long)(packed ? 128 * ((F + 63) / 64) : 2 * F) * K, d_group = (long long)N * F;
   if (tall)
     rc = launch_grouped<4, 2, 2, 2, true, __nv_bfloat16>(grid_f, stream, "moe_gate_up_grouped", hh, K, zero, rp, top, wgu,
-                                                        gu_group, a, F, zero, F, K, te, t0, tr, nt, 0, kind, limit, packed);
+                                                        gu_group, a, F, zero, F, K, te, t0, tr, nt, 0, kind, limit, packed, in_scale);
   else
     rc = launch_grouped<1, 4, 1, 1, true, __nv_bfloat16>(grid_f, stream, "moe_gate_up_grouped", hh, K, zero, rp, top, wgu,
-                                                        gu_group, a, F, zero, F, K, te, t0, tr, nt, 0, kind, limit, packed);
+                                                        gu_group, a, F, zero, F, K, te, t0, tr, nt, 0, kind, limit, packed, in_scale);
   if (rc != GB_OK) return rc;
   const __nv_bfloat16* ac = a;
   if (tall)
     rc = launch_grouped<4, 2, 2, 2, false, float>(grid_n, stream, "moe_down_grouped", ac, F, zero, none, 1, wd, d_group, y, N,
-                                                 zero, N, F, te, t0, tr, nt, 0, 0, 0.f, 0);
+                                                 zero, N, F, te, t0, tr, nt, 0, 0, 0.f, 0, no_scale);
   else
     rc = launch_grouped<1, 4, 1, 1, false, float>(grid_n, stream, "moe_down_grouped", ac, F, zero, none, 1, wd, d_group, y, N,
-                                                 zero, N, F, te, t0, tr, nt, 0, 0, 0.f, 0);
+                                                 zero, N, F, te, t0, tr, nt, 0, 0, 0.f, 0, no_scale);
   if (rc != GB_OK) return rc;
-  moe_combine_kernel<<<T, 256, 0, stream>>>(y, pair_row, weights, x, top, N, alpha);
+  moe_combine_kernel<<<T, 256, 0, stream>>>(y, pair_row, out_weights, x, top, N, alpha);
   return gb::check_launch("moe_combine");
 }
 
@@ -332,15 +342,30 @@ moe_sort_padded_kernel(const int32_t* __restrict__ ids, int R, int E, int gu_row
   }
 }
 
-// a[pair_row[p]] = h[p / top] (rows of K bfloat16, K a multiple of 8), one block per pair
+// a[pair_row[p]] = h[p / top] (rows of K bfloat16, K a multiple of 8), one block per pair; with
+// in_scale the row is multiplied by in_scale[p] (32-bit, rounded once)
 __global__ void __launch_bounds__(128)
 moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ h, const int32_t* __restrict__ pair_row, int top, int K,
-                       __nv_bfloat16* __restrict__ a) {
+                       __nv_bfloat16* __restrict__ a, const float* __restrict__ in_scale) {
   const int p = blockIdx.x, row = pair_row[p];
   if (row < 0) return;
   const uint4* src = reinterpret_cast<const uint4*>(h + (size_t)(p / top) * K);
   uint4* dst = reinterpret_cast<uint4*>(a + (size_t)row * K);
-  for (int c = threadIdx.x; c < K / 8; c += blockDim.x) dst[c] = src[c];
+  if (in_scale == nullptr) {
+    for (int c = threadIdx.x; c < K / 8; c += blockDim.x) dst[c] = src[c];
+    return;
+  }
+  const float s = in_scale[p];
+  for (int c = threadIdx.x; c < K / 8; c += blockDim.x) {
+    uint4 v = src[c];
+    __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(pairs[i]);
+      pairs[i] = __floats2bfloat162_rn(f.x * s, f.y * s);
+    }
+    dst[c] = v;
+  }
 }
 
 }  // namespace
@@ -351,7 +376,8 @@ GB_EXPORT long long gb_moe_padded_rows(long long R, int E) { return ((R + BLOCK_
 // For the tcgen05 grouped products: pairs sorted by expert into blocks of 128 rows, the tokens' rows
 // gathered (padding rows zero). index: pair_row [R], then block_w_gu and block_w_dn [rows / 128 each].
 GB_EXPORT int gb_moe_padded_prepare(const void* h, const int32_t* ids, int T, int top, int E, int K, int gu_rows,
-                                    int dn_rows, int32_t* index, void* a_sorted, cudaStream_t stream) {
+                                    int dn_rows, int32_t* index, void* a_sorted, const float* in_scale,
+                                    cudaStream_t stream) {
   if (T <= 0) return GB_OK;
   if (K % 8 || E < 1 || (size_t)E * 2 * sizeof(int32_t) > 40 * 1024)
     return gb::fail(GB_UNSUPPORTED, "moe_padded_prepare: width %d, %d experts", K, E);
@@ -366,7 +392,7 @@ GB_EXPORT int gb_moe_padded_prepare(const void* h, const int32_t* ids, int T, in
                                                                                       pair_row, block_w_gu, block_w_dn);
   int rc = gb::check_launch("moe_sort_padded");
   if (rc != GB_OK) return rc;
-  moe_gather_rows_kernel<<<(unsigned)R, 128, 0, stream>>>((const __nv_bfloat16*)h, pair_row, top, K, (__nv_bfloat16*)a_sorted);
+  moe_gather_rows_kernel<<<(unsigned)R, 128, 0, stream>>>((const __nv_bfloat16*)h, pair_row, top, K, (__nv_bfloat16*)a_sorted, in_scale);
   return gb::check_launch("moe_gather_rows");
 }
 
@@ -393,8 +419,8 @@ GB_EXPORT int gb_grouped_gemm(const void* a, int lda, long long a_group, const v
   if (M >= 48)
     return launch_grouped<4, 2, 2, 2, false, __nv_bfloat16>(dim3((N + GN - 1) / GN, (M + TALL - 1) / TALL, groups), stream,
                                                            "grouped_gemm", aa, lda, a_group, none, 1, ww, w_group, oo, ldo,
-                                                           out_group, N, K, none, none, none, none, M, 0, 0.f, 0);
+                                                           out_group, N, K, none, none, none, none, M, 0, 0.f, 0, (const float*)nullptr);
   return launch_grouped<1, 4, 1, 1, false, __nv_bfloat16>(dim3((N + GN - 1) / GN, (M + SHORT - 1) / SHORT, groups), stream,
                                                          "grouped_gemm", aa, lda, a_group, none, 1, ww, w_group, oo, ldo,
-                                                         out_group, N, K, none, none, none, none, M, 0, 0.f, 0);
+                                                         out_group, N, K, none, none, none, none, M, 0, 0.f, 0, (const float*)nullptr);
 }

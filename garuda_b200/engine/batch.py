@@ -87,3 +87,6 @@ class StepContext:
     step_cache: dict = field(default_factory=dict)
     # a part's last product leaves here the norm it folded in (``CudaOps.linear``'s ``emit_norm``)
     pending_norm: object = None
+    # called as ``layer_probe(i, x)`` after entry ``i`` of the run order with the residual (for
+    # checks of a model layer by layer); None in ordinary steps
+    layer_probe: object = None

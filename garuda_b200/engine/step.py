@@ -49,6 +49,9 @@ class StepRunner:
         self.steps = 0
         self.tokens_run = 0
         self.graphs = None        # DecodeGraphs, when decode steps are replayed from CUDA graphs
+        # ``layer_probe(i, x)``: called after entry i of the run order with the residual, in steps that
+        # are run kernel by kernel (checks of a model layer by layer); None: not called
+        self.layer_probe = None
         # pinned staging for the batch's arrays: two buffers in turn, each with an event that tells
         # when the copy that last read it has run (pinning memory anew for every step costs far more
         # than the copy)
@@ -135,7 +138,7 @@ class StepRunner:
             tokens = len(entries)
         else:
             batch = self.build_batch(requests, new_lens)
-            ctx = StepContext(batch=batch, ws=self.ws, ops=self.ops, dtype=self.dtype)
+            ctx = StepContext(batch=batch, ws=self.ws, ops=self.ops, dtype=self.dtype, layer_probe=self.layer_probe)
             caches = self.cache.layer_caches(batch.block_tables)
             hold = getattr(self.ops, "on_current_stream", None)
             with (hold() if hold is not None else contextlib.nullcontext()):

@@ -87,6 +87,7 @@ class CudaOps:
         self.device = torch.device(device)
         self.core = load_kernel_lib("garuda_core")
         self._mixers = None
+        self._state = None
         self._declare_core()
         # A word of pinned host memory that a kernel whose bounded wait ran out writes its code to (the
         # device reaches pinned host memory directly); ``failed_wait`` reads it without a copy.
@@ -117,6 +118,8 @@ class CudaOps:
         L.gb_last_error.restype = ctypes.c_char_p
         sig = {
             "gb_embedding": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+            "gb_embedding_copies": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
+            "gb_scale_softcap": [c_void_p, c_longlong, c_float, c_float, c_void_p],
             "gb_layernorm": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
             "gb_residual_axpy": [c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
             "gb_rms_add": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_int, c_int, c_void_p],
@@ -135,7 +138,7 @@ class CudaOps:
             "gb_gemm_simple": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
             "gb_attention_simple": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                                    c_int, c_void_p],
+                                    c_int, c_float, c_int, c_int, c_void_p],
             "gb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p],
             "gb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                           c_void_p],
@@ -165,20 +168,54 @@ class CudaOps:
             self._mixers = L
         return self._mixers
 
+    @property
+    def state_lib(self):
+        """The library of the stream-residual and delta-rule kernels, compiled and loaded when a
+        model first needs it."""
+        if self._state is None:
+            L = load_kernel_lib("garuda_state")
+            L.gb_last_error.restype = ctypes.c_char_p
+            for name, argtypes in self._STATE_SIGNATURES.items():
+                fn = getattr(L, name)
+                fn.argtypes = argtypes
+                fn.restype = c_int
+            self._state = L
+        return self._state
+
+    _STATE_SIGNATURES = {
+        "gb_streams_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                               c_void_p],
+        "gb_streams_update": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                              c_float, c_void_p, c_int, c_void_p],
+        "gb_qkv_bias_append": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                               c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "gb_delta_prepare": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p,
+                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                             c_void_p],
+        "gb_delta_conv_state": [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "gb_delta_recurrence": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
+                                c_int, c_void_p, c_void_p],
+        "gb_delta_out": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int,
+                         c_void_p],
+        "gb_delta_decode": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p,
+                            c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int,
+                            c_void_p, c_int, c_void_p],
+    }
+
     _MIXER_SIGNATURES = {
             "gb_latent_append": [c_void_p, c_int, c_void_p, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p,
                                  c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
             "gb_head_gemm": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_int,
                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
-            "gb_route_topk": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+            "gb_route_topk": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                               c_void_p, c_void_p],
             "gb_moe_gate_up": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                               c_int, c_float, c_void_p],
+                               c_int, c_float, c_void_p, c_void_p],
             "gb_moe_down": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                             c_float, c_void_p],
-            "gb_moe_grouped": [c_void_p] * 6 + [c_int] * 7 + [c_float, c_float, c_int] + [c_void_p] * 4,
+            "gb_moe_grouped": [c_void_p] * 6 + [c_int] * 7 + [c_float, c_float, c_int, c_int] + [c_void_p] * 4,
             "gb_moe_padded_prepare": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                      c_void_p],
+                                      c_void_p, c_void_p],
             "gb_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
             "gb_grouped_gemm": [c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_longlong,
                                 c_int, c_int, c_int, c_int, c_void_p],
@@ -226,16 +263,25 @@ class CudaOps:
         return self._inv_freq[rotary]
 
     def embedding(self, table, ids, out, scale: float = 1.0):
-        """``out[t] = table[ids[t]] * scale`` in 32-bit."""
+        """``out[t] = table[ids[t]] * scale`` in 32-bit; ``out [T, S, d]``: the row ``S`` times (a
+        residual of several streams that all start as the embedding's output)."""
         self._on_device(table, ids, out)
         _need(out.dtype == torch.float32 and out.is_contiguous(), "embedding: out must be contiguous float32")
         _need(ids.dtype == torch.int32, "embedding: ids must be int32")
-        _need(table.is_contiguous() and table.shape[1] == out.shape[1], "embedding: widths differ")
+        _need(table.is_contiguous() and table.shape[1] == out.shape[-1], "embedding: widths differ")
         T = ids.shape[0]
         _need(out.shape[0] >= T, "embedding: out has too few rows")
-        self._check(self.core, self.core.gb_embedding(
+        copies = out.shape[1] if out.dim() == 3 else 1
+        self._check(self.core, self.core.gb_embedding_copies(
             table.data_ptr(), _tag(table, "embedding table"), ids.data_ptr(), out.data_ptr(), T,
-            table.shape[1], table.shape[0], float(scale), self._stream()), "embedding")
+            table.shape[1], table.shape[0], float(scale), int(copies), self._stream()), "embedding")
+
+    def scale_softcap(self, x, scale: float = 1.0, cap: float = 0.0):
+        """``x <- x * scale``, then with ``cap`` > 0 ``x <- cap * tanh(x / cap)``; in place, 32-bit."""
+        self._on_device(x)
+        _need(x.dtype == torch.float32 and x.is_contiguous(), "scale_softcap: contiguous float32")
+        self._check(self.core, self.core.gb_scale_softcap(x.data_ptr(), x.numel(), float(scale), float(cap),
+                                                          self._stream()), "scale_softcap")
 
     def rmsnorm(self, x, weight, eps, out, rows=None):
         self._on_device(x, weight, out, rows)
@@ -441,34 +487,43 @@ class CudaOps:
 
     def paged_attention(self, q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out,
                         scale, window, page_size, num_requests, max_q_len, max_kv_len, ws=None, min_q_len=1,
-                        value_dim=None):
+                        value_dim=None, softcap: float = 0.0, keep_first: int = 0, sink: bool = False):
         """``value_dim``: how many of a value row's first channels are the value (``out`` is then
         ``[T, Hq * value_dim]``); None: all ``hd``. A mixer whose keys and values are parts of one
-        cached row passes the same pool for both and the narrower width."""
+        cached row passes the same pool for both and the narrower width; a value pool of its own may
+        have rows of another width than the keys'. ``softcap`` c > 0: scores become ``c tanh(s / c)``.
+        ``keep_first`` n: a windowed query also reads its request's first n positions. ``sink``: one
+        is added to the softmax's denominator (an entry of score zero without a value)."""
         self._on_device(q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out)
         T, Hq, hd = q.shape
         Hkv = k_pool.shape[1]
-        vd = hd if value_dim is None else int(value_dim)
+        v_hd = v_pool.shape[3]
+        vd = v_hd if value_dim is None else int(value_dim)
         _need(q.is_contiguous() and out.is_contiguous() and out.shape == (T, Hq * vd), "attention: q/out shape")
         _need(q.dtype == k_pool.dtype == v_pool.dtype == out.dtype, "attention: one dtype for q, cache and out")
-        _need(tuple(k_pool.shape[1:]) == (Hkv, page_size, hd) and k_pool.shape == v_pool.shape,
-              "attention: pool shape")
-        _need(0 < vd <= hd, "attention: value_dim must be within the row")
+        _need(tuple(k_pool.shape[1:]) == (Hkv, page_size, hd) and tuple(v_pool.shape[:3]) == tuple(k_pool.shape[:3])
+              and k_pool.is_contiguous() and v_pool.is_contiguous(), "attention: pool shape")
+        _need(0 < vd <= v_hd, "attention: value_dim must be within the row")
         _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attention: block table")
-        if (vd < hd and Hkv == 1 and window == 0 and self.tc is not None and q.dtype == torch.bfloat16
+        plain = softcap == 0.0 and keep_first == 0 and not sink and v_hd == hd
+        if not plain and self.tc is not None and q.dtype == torch.bfloat16 and vd == v_hd and self.tc.capped_attention(
+                q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, scale, window, page_size,
+                num_requests, max_q_len, max_kv_len, ws, softcap, keep_first, sink):
+            return
+        if (plain and vd < hd and Hkv == 1 and window == 0 and self.tc is not None and q.dtype == torch.bfloat16
                 and k_pool.data_ptr() == v_pool.data_ptr()
                 and self.tc.latent_attention(q, k_pool, out, block_table, cu_q, kv_lens, vd, scale, page_size,
                                              num_requests, max_q_len, max_kv_len, ws)):
             return          # keys and values are parts of one cached row that every head reads
-        if vd == hd and self.tc is not None and q.dtype == torch.bfloat16 and self.tc.paged_attention(
+        if plain and vd == hd and self.tc is not None and q.dtype == torch.bfloat16 and self.tc.paged_attention(
                 q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, scale, window, page_size,
                 num_requests, max_q_len, max_kv_len, ws, min_q_len):
             return
         self._check(self.core, self.core.gb_attention_simple(
             q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), _tag(q, "attention q"),
             block_table.data_ptr(), block_table.shape[1], cu_q.data_ptr(), kv_lens.data_ptr(),
-            token_req.data_ptr(), out.data_ptr(), T, Hq, Hkv, hd, hd, vd, float(scale), int(window),
-            int(page_size), self._stream()), "attention")
+            token_req.data_ptr(), out.data_ptr(), T, Hq, Hkv, hd, v_hd, vd, float(scale), int(window),
+            int(page_size), float(softcap), int(keep_first), int(bool(sink)), self._stream()), "attention")
 
     # ------------------------------------------------------------------ more norms and residual forms
     def layernorm(self, x, weight, bias, eps, out, rows=None):
@@ -558,9 +613,12 @@ class CudaOps:
         self.gated_act(tmp, act, kind, limit, group)
 
     # ------------------------------------------------------------------ routed experts
-    def route_topk(self, h, w_router, bias, top, ids, weights):
+    ROUTER_SCORES = {"softmax_chosen": 0, "sigmoid": 1}
+
+    def route_topk(self, h, w_router, bias, top, ids, weights, score: str = "softmax_chosen"):
         """Router logits ``h @ w_router^T + bias`` in 32-bit; ``ids[T, top]`` the experts with the
-        largest logits (descending), ``weights[T, top]`` the softmax over those logits only."""
+        largest logits (descending), ``weights[T, top]`` the softmax over those logits only, or
+        (``score`` "sigmoid") each chosen expert's ``sigmoid(logit)``, not renormalized."""
         self._on_device(h, w_router, bias, ids, weights)
         T, K = h.shape
         E = w_router.shape[0]
@@ -570,11 +628,12 @@ class CudaOps:
         _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == E), "route_topk: a float32 bias")
         self._check(self.mixers, self.mixers.gb_route_topk(
             h.data_ptr(), _tag(h, "router input"), w_router.data_ptr(), _ptr(bias), _tag(w_router, "router"),
-            T, E, K, int(top), ids.data_ptr(), weights.data_ptr(), self._stream()), "route_topk")
+            T, E, K, int(top), self.ROUTER_SCORES[score], ids.data_ptr(), weights.data_ptr(), self._stream()), "route_topk")
 
-    def moe_gate_up(self, h, w_gate_up, ids, act, kind: str, limit: float):
+    def moe_gate_up(self, h, w_gate_up, ids, act, kind: str, limit: float, in_scale=None):
         """``act[T, top, F]``: every token's gate/up products against its chosen experts'
-        weights ``w_gate_up[E, 2F, K]`` (gate rows, then up rows), through the activation."""
+        weights ``w_gate_up[E, 2F, K]`` (gate rows, then up rows), through the activation.
+        ``in_scale [T, top]``: a factor on what goes into each chosen expert."""
         self._on_device(h, w_gate_up, ids, act)
         T, K = h.shape
         top = ids.shape[1]
@@ -583,10 +642,12 @@ class CudaOps:
               and w_gate_up.shape[2] == K and act.shape == (T, top, F2 // 2), "moe_gate_up: shapes")
         self._check(self.mixers, self.mixers.gb_moe_gate_up(
             h.data_ptr(), _tag(h, "h"), w_gate_up.data_ptr(), _tag(w_gate_up, "w"), ids.data_ptr(), act.data_ptr(),
-            _tag(act, "act"), T, top, F2 // 2, K, self.GATE_ACTS[kind], float(limit), self._stream()), "moe_gate_up")
+            _tag(act, "act"), T, top, F2 // 2, K, self.GATE_ACTS[kind], float(limit), _ptr(in_scale), self._stream()),
+            "moe_gate_up")
 
     def moe_down(self, act, w_down, ids, weights, x, alpha: float = 1.0):
-        """``x[t] += alpha * sum_j weights[t, j] * (act[t, j] @ w_down[ids[t, j]]^T)``."""
+        """``x[t] += alpha * sum_j weights[t, j] * (act[t, j] @ w_down[ids[t, j]]^T)``; ``weights``
+        None: all one."""
         self._on_device(act, w_down, ids, weights, x)
         T, top, F = act.shape
         E, N, _ = w_down.shape
@@ -594,7 +655,7 @@ class CudaOps:
               and x.dtype == torch.float32 and x.is_contiguous(), "moe_down: shapes")
         self._check(self.mixers, self.mixers.gb_moe_down(
             act.data_ptr(), _tag(act, "act"), w_down.data_ptr(), _tag(w_down, "w"), ids.data_ptr(),
-            weights.data_ptr(), x.data_ptr(), T, top, F, N, float(alpha), self._stream()), "moe_down")
+            _ptr(weights), x.data_ptr(), T, top, F, N, float(alpha), self._stream()), "moe_down")
 
     def pack_expert_gate_up(self, gates, ups):
         """The experts' gate and up matrices stacked, in the layout ``routed_feed_forward`` wants:
@@ -611,15 +672,17 @@ class CudaOps:
     GROUPED_TC_PAIRS = 1024
 
     def routed_feed_forward(self, ctx, h, w_gate_up, w_down, ids, weights, x, kind: str, limit: float,
-                            alpha: float = 1.0):
+                            alpha: float = 1.0, scale_input: bool = False):
         """``x[t] += alpha * sum_j weights[t, j] * expert_{ids[t, j]}(h[t])`` with the experts'
-        weights stacked: ``w_gate_up`` from ``pack_expert_gate_up``, ``w_down [E, N, F]``."""
+        weights stacked: ``w_gate_up`` from ``pack_expert_gate_up``, ``w_down [E, N, F]``.
+        ``scale_input``: the weight multiplies what goes into the expert instead,
+        ``sum_j expert(weights[t, j] * h[t])``."""
         T, top = ids.shape
         E, N, F = w_down.shape
         K = h.shape[1]
         packed = getattr(w_gate_up, "gb_group", 0) == 64
         if packed and T * top >= self.GROUPED_TC_PAIRS and self._routed_tcgen05(ctx, h, w_gate_up, w_down, ids, weights,
-                                                                               x, kind, limit, alpha):
+                                                                               x, kind, limit, alpha, scale_input):
             return
         if packed:
             # on the tensor cores: pairs sorted by expert on the device, two grouped products, a weighted sum
@@ -636,14 +699,14 @@ class CudaOps:
             y = ctx.ws.get("expert_rows", (T * top, N), torch.float32)
             self._check(L, L.gb_moe_grouped(
                 h.data_ptr(), w_gate_up.data_ptr(), w_down.data_ptr(), ids.data_ptr(), weights.data_ptr(), x.data_ptr(),
-                T, top, E, F, K, N, self.GATE_ACTS[kind], float(limit), float(alpha), 1, index.data_ptr(), act.data_ptr(),
-                y.data_ptr(), self._stream()), "moe_grouped", 4)
+                T, top, E, F, K, N, self.GATE_ACTS[kind], float(limit), float(alpha), 1, int(scale_input), index.data_ptr(),
+                act.data_ptr(), y.data_ptr(), self._stream()), "moe_grouped", 4)
             return
         act = ctx.ws.get("expert_act", (T, top, F), h.dtype)
-        self.moe_gate_up(h, w_gate_up, ids, act, kind, limit)
-        self.moe_down(act, w_down, ids, weights, x, alpha)
+        self.moe_gate_up(h, w_gate_up, ids, act, kind, limit, weights if scale_input else None)
+        self.moe_down(act, w_down, ids, None if scale_input else weights, x, alpha)
 
-    def _routed_tcgen05(self, ctx, h, w_gate_up, w_down, ids, weights, x, kind, limit, alpha) -> bool:
+    def _routed_tcgen05(self, ctx, h, w_gate_up, w_down, ids, weights, x, kind, limit, alpha, scale_input=False) -> bool:
         """Many pairs: sorted by expert into blocks of 128 rows (padding rows zero), then the two
         products on the tcgen05 many-token kernel with each block's expert read from a list."""
         T, top = ids.shape
@@ -666,12 +729,13 @@ class CudaOps:
         index = ctx.ws.get("expert_index_padded", (T * top + 2 * blocks,), torch.int32)
         y = ctx.ws.get("expert_rows_padded", (rows, N), torch.float32)
         self._check(L, L.gb_moe_padded_prepare(h.data_ptr(), ids.data_ptr(), T, top, E, K, gu_rows, N, index.data_ptr(),
-                                               a.data_ptr(), self._stream()), "moe_padded_prepare", 2)
+                                               a.data_ptr(), weights.data_ptr() if scale_input else None,
+                                               self._stream()), "moe_padded_prepare", 2)
         block_gu = index.data_ptr() + 4 * T * top
         block_dn = block_gu + 4 * blocks
         tc.grouped(a, w_gate_up, act, F, E, block_gu, 2, gate_act=self.GATE_ACTS[kind], gate_limit=limit)
         tc.grouped(act, w_down, y, N, E, block_dn, 0)
-        self._check(L, L.gb_moe_combine(y.data_ptr(), index.data_ptr(), weights.data_ptr(), x.data_ptr(), T, top, N,
+        self._check(L, L.gb_moe_combine(y.data_ptr(), index.data_ptr(), None if scale_input else weights.data_ptr(), x.data_ptr(), T, top, N,
                                         float(alpha), self._stream()), "moe_combine")
         return True
 
@@ -759,6 +823,121 @@ class CudaOps:
             a.data_ptr(), _tag(a, "a"), a.stride(0), a.stride(1), w.data_ptr(), _tag(w, "w"), n * k, w_n, w_k,
             out.data_ptr(), _tag(out, "out"), out.stride(0), out.stride(1), T, H, int(n), int(k), int(tail),
             self._stream()), "head_linear")
+
+    # ------------------------------------------------------------------ a residual of several streams
+    #: a stream write may compute the next sublayer's normed input in the same pass
+    fuses_stream_reads = True
+
+    def streams_rmsnorm(self, x, in_w, weight, eps, out, rows=None):
+        """``out[r] = rms(sum_s in_w[s] x[row, s]) * weight`` for ``x [T, S, d]`` (32-bit); ``rows``:
+        only these rows of ``x``."""
+        self._on_device(x, in_w, weight, out, rows)
+        _need(x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 3, "streams_rmsnorm: x must be float32 [T, S, d]")
+        T, S, d = x.shape
+        _need(in_w.dtype == torch.float32 and in_w.numel() == S and weight.numel() == d and out.shape[1] == d
+              and out.is_contiguous(), "streams_rmsnorm: shapes")
+        n = T if rows is None else rows.shape[0]
+        _need(out.shape[0] == n and (rows is None or rows.dtype == torch.int32), "streams_rmsnorm: rows")
+        L = self.state_lib
+        self._check(L, L.gb_streams_rmsnorm(x.data_ptr(), in_w.data_ptr(), weight.data_ptr(), _tag(weight, "norm weight"),
+                                            float(eps), out.data_ptr(), _tag(out, "streams_rmsnorm out"), _ptr(rows), n, S, d,
+                                            self._stream()), "streams_rmsnorm")
+
+    def streams_update(self, x, mix, out_w, y, next_in=None, norm_weight=None, eps: float = 0.0, normed=None):
+        """``x[t, j] <- sum_s mix[s, j] x[t, s] + out_w[j] y[t]`` for all ``j`` at once (``x [T, S, d]``,
+        ``y [T, d]``, 32-bit). With ``next_in``: also ``normed[t] = rms(sum_s next_in[s] x[t, s]) *
+        norm_weight`` of the new streams, in the same pass."""
+        self._on_device(x, mix, out_w, y, next_in, norm_weight, normed)
+        _need(x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 3, "streams_update: x must be float32 [T, S, d]")
+        T, S, d = x.shape
+        _need(y.dtype == torch.float32 and y.is_contiguous() and tuple(y.shape) == (T, d), "streams_update: y must be float32 [T, d]")
+        _need(mix.dtype == torch.float32 and out_w.dtype == torch.float32 and mix.numel() == S * S and out_w.numel() == S
+              and mix.is_contiguous(), "streams_update: weights")
+        L = self.state_lib
+        if next_in is None:
+            self._check(L, L.gb_streams_update(x.data_ptr(), mix.data_ptr(), out_w.data_ptr(), y.data_ptr(), T, S, d, None,
+                                               None, GB_F32, 0.0, None, GB_F32, self._stream()), "streams_update")
+            return
+        _need(next_in.dtype == torch.float32 and next_in.numel() == S and norm_weight.numel() == d
+              and tuple(normed.shape) == (T, d) and normed.is_contiguous(), "streams_update: the next read")
+        self._check(L, L.gb_streams_update(x.data_ptr(), mix.data_ptr(), out_w.data_ptr(), y.data_ptr(), T, S, d,
+                                           next_in.data_ptr(), norm_weight.data_ptr(), _tag(norm_weight, "norm weight"),
+                                           float(eps), normed.data_ptr(), _tag(normed, "normed"), self._stream()),
+                    "streams_update")
+
+    def qkv_bias_append(self, qkv, bias, q_out, k_pool, v_pool, positions, token_req, block_table, heads, kv_heads,
+                        head_dim, value_dim, page_size):
+        """Split ``qkv [T, heads * head_dim + kv_heads * (head_dim + value_dim)]`` (+ ``bias``):
+        queries to ``q_out [T, heads, head_dim]``, keys (``head_dim`` wide) and values (``value_dim``
+        wide) into their pages. Nothing is rotated."""
+        self._on_device(qkv, bias, q_out, k_pool, v_pool, positions, token_req, block_table)
+        T = qkv.shape[0]
+        cols = heads * head_dim + kv_heads * (head_dim + value_dim)
+        _need(qkv.is_contiguous() and qkv.shape[1] == cols, "qkv_bias_append: qkv has the wrong width")
+        _need(bias is None or (bias.numel() == cols and bias.is_contiguous()), "qkv_bias_append: bias")
+        _need(q_out.is_contiguous() and tuple(q_out.shape) == (T, heads, head_dim), "qkv_bias_append: q_out shape")
+        _need(k_pool.dtype == q_out.dtype == v_pool.dtype and k_pool.is_contiguous() and v_pool.is_contiguous()
+              and tuple(k_pool.shape[1:]) == (kv_heads, page_size, head_dim)
+              and tuple(v_pool.shape[1:]) == (kv_heads, page_size, value_dim), "qkv_bias_append: pool shapes")
+        _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and positions.dtype == torch.int32
+              and token_req.dtype == torch.int32, "qkv_bias_append: int32 indices")
+        L = self.state_lib
+        self._check(L, L.gb_qkv_bias_append(
+            qkv.data_ptr(), _tag(qkv, "qkv"), _ptr(bias), _tag(bias, "bias") if bias is not None else GB_F32,
+            q_out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), _tag(q_out, "q_out"), positions.data_ptr(),
+            token_req.data_ptr(), block_table.data_ptr(), block_table.shape[1], T, heads, kv_heads, head_dim,
+            value_dim, page_size, self._stream()), "qkv_bias_append")
+
+    # ------------------------------------------------------------------ gated delta rule with channel decay
+    def delta_rule(self, ctx, proj, second, conv_w, a_log, dt_bias, norm_w, eps, state, heads, kv_heads, dim, vdim,
+                   taps, out):
+        """The recurrent part of a delta-rule mixer for one step. ``proj [T, 2 G dim + H vdim + H]``
+        (32-bit: q | k | v before their convolution, beta's logit), ``second [T, H dim + H vdim]``
+        (32-bit: the decay's pre-activation, the output gate's logit), ``conv_w [2 G dim + H vdim,
+        taps]``, ``state [slots, H dim vdim + (taps - 1) (2 G dim + H vdim)]`` (32-bit: S, then the
+        kept last inputs of the convolution). ``out [T, H vdim]``: every head's read-out, divided by its
+        root mean square, times ``norm_w`` and the gate. Advances the state of the batch's requests."""
+        b = ctx.batch
+        self._on_device(proj, second, conv_w, a_log, dt_bias, norm_w, state, out)
+        T = proj.shape[0]
+        H, G = int(heads), int(kv_heads)
+        C = 2 * G * dim + H * vdim
+        n_state = H * dim * vdim
+        _need(proj.dtype == torch.float32 and proj.is_contiguous() and proj.shape[1] == C + H, "delta_rule: proj")
+        _need(second.dtype == torch.float32 and second.is_contiguous() and second.shape[1] == H * dim + H * vdim,
+              "delta_rule: second")
+        _need(conv_w.is_contiguous() and tuple(conv_w.shape) == (C, taps) and a_log.numel() == H and dt_bias.numel() == H * dim
+              and norm_w.numel() == vdim and conv_w.dtype == a_log.dtype == dt_bias.dtype == norm_w.dtype, "delta_rule: weights")
+        _need(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == n_state + (taps - 1) * C,
+              "delta_rule: state")
+        _need(out.is_contiguous() and tuple(out.shape) == (T, H * vdim), "delta_rule: out")
+        L = self.state_lib
+        stride = state.shape[1]
+        conv_state = state.data_ptr() + 4 * n_state
+        wt = _tag(conv_w, "delta_rule weights")
+        if b.max_q_len == 1 and vdim <= 256:
+            # single tokens: one kernel for everything but the shift of the kept inputs
+            self._check(L, L.gb_delta_decode(
+                proj.data_ptr(), proj.shape[1], second.data_ptr(), second.shape[1], conv_w.data_ptr(), wt, taps, conv_state,
+                stride, a_log.data_ptr(), dt_bias.data_ptr(), norm_w.data_ptr(), float(eps), b.slots.data_ptr(),
+                state.data_ptr(), stride, T, H, G, dim, vdim, out.data_ptr(), _tag(out, "delta_rule out"), self._stream()),
+                "delta_decode")
+        else:
+            W = C + H * dim + H
+            prep = ctx.ws.get("delta_prep", (T, W), torch.float32)
+            o = ctx.ws.get("delta_o", (T, H * vdim), torch.float32)
+            self._check(L, L.gb_delta_prepare(
+                proj.data_ptr(), proj.shape[1], second.data_ptr(), second.shape[1], conv_w.data_ptr(), wt, taps, conv_state,
+                stride, a_log.data_ptr(), dt_bias.data_ptr(), b.token_req.data_ptr(), b.cu_q.data_ptr(), b.slots.data_ptr(),
+                prep.data_ptr(), W, T, H, G, dim, vdim, self._stream()), "delta_prepare")
+            self._check(L, L.gb_delta_recurrence(
+                prep.data_ptr(), W, b.cu_q.data_ptr(), b.slots.data_ptr(), state.data_ptr(), stride, b.num_requests, H, G,
+                dim, vdim, o.data_ptr(), self._stream()), "delta_recurrence")
+            self._check(L, L.gb_delta_out(
+                o.data_ptr(), second.data_ptr(), second.shape[1], H * dim, norm_w.data_ptr(), wt, float(eps), out.data_ptr(),
+                _tag(out, "delta_rule out"), T, H, vdim, self._stream()), "delta_out")
+        self._check(L, L.gb_delta_conv_state(proj.data_ptr(), proj.shape[1], conv_state, stride, b.cu_q.data_ptr(),
+                                             b.slots.data_ptr(), b.num_requests, C, taps, self._stream()), "delta_conv_state")
 
     # ------------------------------------------------------------------ sampling
     def argmax(self, logits, out):

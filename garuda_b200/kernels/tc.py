@@ -272,6 +272,12 @@ class TensorCoreKernels:
         self.ops._check(lib, code, "attention_mma", (1 if has_decode else 0) + (1 if max_q_len * g > 16 else 0))
         return True
 
+    def capped_attention(self, q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, scale, window,
+                         page_size, num_requests, max_q_len, max_kv_len, ws, softcap, keep_first, sink) -> bool:
+        """Attention with capped scores, kept first positions, a sink or values of another width
+        than the keys on the tensor cores; False where no such kernel takes the shape."""
+        return False
+
     # ------------------------------------------------------------------ attention over cached latent rows
     @staticmethod
     def takes_latent(rank: int, rot: int) -> bool:

@@ -47,6 +47,11 @@ class ModelSpec:
     head: Optional[str]                  # tensor name of the [vocab, width] head; None: tied
     embedding_init: Tuple = ("normal", 0.02)
     embedding_scale: float = 1.0         # the embedding's output is the table's row times this
+    # the residual as several streams [T, streams, width], all equal to the embedding's output at the
+    # start, summed before the final norm; None: one residual [T, width]
+    streams: Optional[int] = None
+    logit_scale: float = 1.0             # logits = head(x) * logit_scale ...
+    logit_softcap: Optional[float] = None   # ... then c * tanh(logits / c)
     # tensors of the model itself that no part owns (what ``LayerCall.add_row`` names): name -> spec
     extra_tensors: Optional[Dict[str, TensorSpec]] = None
     eos_token_ids: Tuple[int, ...] = ()  # generation ends on any of them (config.json may list several)
@@ -140,6 +145,8 @@ class Decoder:
         logits ``[W, vocab]`` for the batch's ``logit_rows`` only: the final norm
         and the head touch no other row (garuda/src/llama/mod.rs:1110-1113)."""
         b, ops, s = ctx.batch, self.ops, self.spec
+        if s.streams is not None:
+            return self._forward_streams(ctx, layer_caches)
         x = ctx.ws.get("residual", (b.num_tokens, s.width), torch.float32)
         if s.embedding_scale != 1.0:
             ops.embedding(self.embedding, b.token_ids, x, s.embedding_scale)
@@ -163,9 +170,35 @@ class Decoder:
                 pending = block.forward(ctx, x, layer_caches[i], pending=pending, next_norm=next_norm)
             else:
                 pending = block.forward(ctx, x, layer_caches[i])
+            if ctx.layer_probe is not None:
+                ctx.layer_probe(i, x)
+        return self._logits(ctx, x)
+
+    def _logits(self, ctx, x) -> torch.Tensor:
+        b, ops, s = ctx.batch, self.ops, self.spec
         w = b.num_logit_rows
         logits = ctx.ws.get("logits", (w, s.vocab_size), torch.float32)
         if w:
             z = self.final_norm.forward(ctx, x, rows=b.logit_rows, out_name="final_normed")
             ops.linear(z, self.head, logits)
+            if s.logit_scale != 1.0 or s.logit_softcap:
+                ops.scale_softcap(logits, s.logit_scale, s.logit_softcap or 0.0)
         return logits
+
+    def _forward_streams(self, ctx, layer_caches) -> torch.Tensor:
+        """The run order over a residual of several streams. A layer's last write to the streams
+        computes the next layer's first normed input in the same pass where the kernels can."""
+        b, ops, s = ctx.batch, self.ops, self.spec
+        if any(call.add_embedding or call.add_row is not None for call in s.order):
+            raise ValueError("a residual of several streams takes no additions between layer calls")
+        x = ctx.ws.get("residual", (b.num_tokens, s.streams, s.width), torch.float32)
+        ops.embedding(self.embedding, b.token_ids, x, s.embedding_scale)
+        normed = None
+        for i, call in enumerate(s.order):
+            block = self.blocks[call.layer]
+            nxt = self.blocks[s.order[i + 1].layer] if i + 1 < len(s.order) else None
+            then = nxt.first_read() if nxt is not None and ctx.layer_probe is None else None
+            normed = block.forward(ctx, x, layer_caches[i], normed=normed, then=then)
+            if ctx.layer_probe is not None:
+                ctx.layer_probe(i, x)
+        return self._logits(ctx, x)

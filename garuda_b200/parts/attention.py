@@ -117,3 +117,77 @@ class PagedAttention(Mixer):
         y = ws.get("mixer_out", (T, self.width), torch.float32)
         ops.linear(out, self.w_o, y)
         return y
+
+
+@register_mixer("capped_sink_attention")
+class CappedSinkAttention(Mixer):
+    """Grouped-query attention over the paged cache with keys and values of widths of their own,
+    optional biases on the three projections, and no position encoding: positions enter only
+    through the mask. With ``q, k, v`` the projected rows (``dim`` wide for queries and keys,
+    ``vdim`` for values), query head ``h`` reading key/value head ``h // (heads / kv_heads)``:
+
+        s_ij = (q_i . k_j) * scale;          softcap c:  s_ij <- c tanh(s_ij / c)
+        i reads j  iff  j <= i and (i - j < window  or  j < keep_first)
+        sink:  p_ij = exp(s_ij) / (1 + sum_j' exp(s_ij'))    (else the ordinary softmax)
+        out_i = W_o concat_h sum_j p_ij v_j
+
+    ``names``: the tensors' local names (``q, k, v, o``; a bias is the weight's name with ``.b``
+    added). Kept positions keep their true places: nothing is renumbered."""
+    graph_safe = True
+
+    def __init__(self, width: int, heads: int, kv_heads: int, dim: int, vdim: Optional[int] = None,
+                 scale: Optional[float] = None, softcap: Optional[float] = None, window: Optional[int] = None,
+                 keep_first: int = 0, sink: bool = False, bias: bool = False, names: Optional[dict] = None,
+                 init_std: float = 0.02):
+        if heads % kv_heads:
+            raise ValueError(f"{heads} query heads are not a multiple of {kv_heads} kv heads")
+        self.width, self.heads, self.kv_heads, self.dim = int(width), int(heads), int(kv_heads), int(dim)
+        self.vdim = int(vdim) if vdim else self.dim
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.dim)
+        self.softcap = float(softcap) if softcap else 0.0
+        self.window = int(window) if window else None
+        self.keep_first = int(keep_first or 0) if self.window else 0
+        self.sink, self.bias = bool(sink), bool(bias)
+        self.names = dict({"q": "q", "k": "k", "v": "v", "o": "o"}, **(names or {}))
+        self.init_std = float(init_std)
+        self.q_dim, self.k_dim, self.v_dim = self.heads * self.dim, self.kv_heads * self.dim, self.kv_heads * self.vdim
+
+    def tensors(self):
+        init, n = ("normal", self.init_std), self.names
+        t = {n["q"]: TensorSpec((self.q_dim, self.width), init=init), n["k"]: TensorSpec((self.k_dim, self.width), init=init),
+             n["v"]: TensorSpec((self.v_dim, self.width), init=init),
+             n["o"]: TensorSpec((self.width, self.heads * self.vdim), init=init)}
+        if self.bias:
+            for key, rows in (("q", self.q_dim), ("k", self.k_dim), ("v", self.v_dim)):
+                t[n[key] + ".b"] = TensorSpec((rows,), role="vector", init=("normal", 0.02))
+        return t
+
+    def cache_need(self):
+        return PagedKV(self.kv_heads, self.dim, self.window, value_dim=self.vdim, keep_first=self.keep_first)
+
+    def load(self, tensors, ops, dtype):
+        super().load(tensors, ops, dtype)
+        n = self.names
+        self.w_qkv = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0).contiguous()
+        self.b_qkv = (torch.cat([tensors[n[k] + ".b"].float() for k in ("q", "k", "v")]).contiguous()
+                      if self.bias else None)
+        self.w_o = tensors[n["o"]].contiguous()
+
+    def forward(self, ctx, h, cache, residual=None):
+        b, ops, ws = ctx.batch, self.ops, ctx.ws
+        T = h.shape[0]
+        qkv = ws.get("qkv", (T, self.w_qkv.shape[0]), torch.float32)
+        ops.linear(h, self.w_qkv, qkv)
+        q = ws.get("q_heads", (T, self.heads, self.dim), self.dtype)
+        ops.qkv_bias_append(qkv, self.b_qkv, q, cache.k, cache.v, b.positions, b.token_req, cache.block_table,
+                            self.heads, self.kv_heads, self.dim, self.vdim, cache.page_size)
+        out = ws.get("attn_ctx", (T, self.heads * self.vdim), self.dtype)
+        ops.paged_attention(q, cache.k, cache.v, cache.block_table, b.cu_q, b.kv_lens, b.token_req, out,
+                            self.scale, self.window or 0, cache.page_size, b.num_requests, b.max_q_len, b.max_kv_len,
+                            ws=ws, min_q_len=b.min_q_len, softcap=self.softcap, keep_first=self.keep_first, sink=self.sink)
+        if residual is not None:
+            ops.linear(out, self.w_o, residual, accumulate=True)
+            return None
+        y = ws.get("mixer_out", (T, self.width), torch.float32)
+        ops.linear(out, self.w_o, y)
+        return y

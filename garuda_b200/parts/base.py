@@ -30,20 +30,35 @@ class TensorSpec:
     contraction or an embedding table: held in the compute dtype), ``"vector"``
     (a norm weight or the like: a tensor stored in 32-bit stays 32-bit) or
     ``"table"`` (integers: held as int32). ``init`` describes the random-weights
-    mode: ``("normal", std)``, ``("ones",)`` or ``("normal_about_one", std)``."""
-    shape: Tuple[int, ...]
+    mode: ``("normal", std)``, ``("ones",)`` or ``("normal_about_one", std)``. A size that
+    the configuration does not give (the rank of a low-rank pair of matrices) is written ``None``
+    in ``shape``: the loader takes what the file has there and checks the other sizes;
+    random weights use ``free`` for it."""
+    shape: Tuple[Optional[int], ...]
     role: str = "matrix"
     init: Tuple = ("normal", 0.02)
+    free: int = 16
+
+    def fits(self, shape) -> bool:
+        return len(shape) == len(self.shape) and all(w is None or int(w) == int(s) for w, s in zip(self.shape, shape))
+
+    def concrete(self) -> Tuple[int, ...]:
+        return tuple(self.free if s is None else int(s) for s in self.shape)
 
 
 @dataclass(frozen=True)
 class PagedKV:
     """A mixer that keeps one key and one value vector per position.
     ``window``: positions a query may look back over, itself included
-    (garuda/src/cache/mod.rs:333-338); ``None`` keeps everything."""
+    (garuda/src/cache/mod.rs:333-338); ``None`` keeps everything. ``value_dim``: the width of
+    a value vector where it differs from the key's (``None``: ``head_dim``). ``keep_first``: with a
+    window, the first positions of a request that every later query still reads; their pages stay
+    with the request while the pages between them and the window go back to the pool."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -150,6 +165,18 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Connection(Part):
+    """How a sublayer is joined to a residual that is kept as several streams ``x [T, S, d]``
+    (32-bit): ``read`` gives the sublayer's normed input, ``write`` takes its output ``y [T, d]``
+    (32-bit) and updates every stream."""
+
+    def read(self, ctx, x: torch.Tensor, norm) -> torch.Tensor:
+        raise NotImplementedError
+
+    def write(self, ctx, x: torch.Tensor, y: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
 class ResidualBranch(Part):
     """Something a layer adds to the residual stream after its mixer and feed-forward, computed
     from the stream itself and the step's tokens (a per-layer token embedding, gated): it reads
@@ -166,6 +193,7 @@ class ResidualBranch(Part):
 
 _REGISTRIES: Dict[str, Dict[str, Callable]] = {
     "mixer": {}, "feed_forward": {}, "norm": {}, "position_encoding": {}, "block": {}, "branch": {},
+    "connection": {},
 }
 
 
@@ -182,6 +210,7 @@ def register_norm(name, cls=None): return _register("norm", name, cls)
 def register_position_encoding(name, cls=None): return _register("position_encoding", name, cls)
 def register_block(name, cls=None): return _register("block", name, cls)
 def register_branch(name, cls=None): return _register("branch", name, cls)
+def register_connection(name, cls=None): return _register("connection", name, cls)
 
 
 @dataclass(frozen=True)

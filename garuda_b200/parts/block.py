@@ -27,6 +27,9 @@ class BlockSpec:
     arrangement: str = "pre_norm"
     residual_mult: float = 1.0                 # x += residual_mult * part(norm(x))
     branches: Tuple[PartSpec, ...] = ()        # after the feed-forward, in order
+    # for an arrangement over a residual of several streams: how each sublayer is joined to them
+    mixer_connection: Optional[PartSpec] = None
+    feed_forward_connection: Optional[PartSpec] = None
 
 
 @register_block("pre_norm")

@@ -7,6 +7,12 @@ weights, and an optional shared expert runs for every token.
     expert(h) = W_down act(W_gate h, W_up h)  (``act`` as in ``GatedFeedForward``)
     out    = sum_chosen weight_e * expert_e(h) + shared(h)
 
+Variants, by constructor parameter: ``router_score="sigmoid"`` weighs a chosen expert by
+``sigmoid(z_e)`` (the choice is still of the largest; nothing is renormalized);
+``scale_input=True`` puts the weight on what goes into the expert, ``out = sum_chosen
+expert_e(weight_e * h)``; ``router_bias=False`` drops ``b_r``; ``activation="silu"`` is the plain
+SiLU gate.
+
 Tensor names: ``router``, ``router.b``, ``e<i>.gate|up|down``, ``shared.gate|up|down``.
 """
 from __future__ import annotations
@@ -25,7 +31,11 @@ class RoutedExperts(FeedForward):
 
     def __init__(self, width: int, experts: int, top: int, inner: int, activation: str = "clamped_swish",
                  limit: float = 0.0, shared_inner: Optional[int] = None, shared_limit: float = 0.0,
-                 router_bias: bool = True, init_std: float = 0.02):
+                 router_bias: bool = True, init_std: float = 0.02, router_score: str = "softmax_chosen",
+                 scale_input: bool = False):
+        if router_score not in ("softmax_chosen", "sigmoid"):
+            raise ValueError(f"unknown router score {router_score!r}")
+        self.router_score, self.scale_input = router_score, bool(scale_input)
         if not 1 <= top <= experts:
             raise ValueError(f"a token uses 1 to {experts} experts, got {top}")
         self.width, self.experts, self.top, self.inner = int(width), int(experts), int(top), int(inner)
@@ -73,9 +83,14 @@ class RoutedExperts(FeedForward):
             alpha = 1.0
         ids = ws.get("expert_ids", (T, self.top), torch.int32)
         weights = ws.get("expert_weights", (T, self.top), torch.float32)
-        ops.route_topk(h, self.w_router, self.b_router, self.top, ids, weights)
-        ops.routed_feed_forward(ctx, h, self.w_gate_up, self.w_down, ids, weights, target, self.activation,
-                                self.limit, alpha)
+        if self.router_score == "softmax_chosen" and not self.scale_input:
+            ops.route_topk(h, self.w_router, self.b_router, self.top, ids, weights)
+            ops.routed_feed_forward(ctx, h, self.w_gate_up, self.w_down, ids, weights, target, self.activation,
+                                    self.limit, alpha)
+        else:
+            ops.route_topk(h, self.w_router, self.b_router, self.top, ids, weights, score=self.router_score)
+            ops.routed_feed_forward(ctx, h, self.w_gate_up, self.w_down, ids, weights, target, self.activation,
+                                    self.limit, alpha, scale_input=self.scale_input)
         if self.shared_inner:
             act = ws.get("shared_act", (T, self.shared_inner), self.dtype)
             ops.linear_gated(ctx, h, self.w_shared_gate_up, act, self.activation, self.shared_limit)

@@ -17,19 +17,30 @@ from .base import Norm, TensorSpec, register_norm
 
 @register_norm("rms")
 class RMSNorm(Norm):
+    """``weight_name``: the tensor's local name. ``unit_offset``: the stored weight lies about
+    zero and the norm multiplies by ``1 + weight`` (the sum is taken once, in 32-bit, when the
+    weights are loaded). A residual kept as several streams ``x [T, S, d]`` is normed as the
+    weighted sum of its streams (``stream_weights [S]``; None: the plain sum)."""
     graph_safe = True
 
-    def __init__(self, width: int, eps: float, weight_init=("ones",)):
+    def __init__(self, width: int, eps: float, weight_init=("ones",), weight_name: str = "weight",
+                 unit_offset: bool = False):
         self.width = int(width)
         self.eps = float(eps)
-        self.weight_init = tuple(weight_init)
+        self.weight_name = weight_name
+        self.unit_offset = bool(unit_offset)
+        self.weight_init = ("normal", 0.1) if self.unit_offset and tuple(weight_init) == ("ones",) else tuple(weight_init)
 
     def tensors(self):
-        return {"weight": TensorSpec((self.width,), role="vector", init=self.weight_init)}
+        return {self.weight_name: TensorSpec((self.width,), role="vector", init=self.weight_init)}
 
     def load(self, tensors, ops, dtype):
         super().load(tensors, ops, dtype)
-        self.weight = tensors["weight"]
+        self.weight = tensors[self.weight_name]
+        if self.unit_offset:
+            self.weight = (1.0 + self.weight.float()).contiguous()
+        self._weight32 = None
+        self._ones = {}
 
     def fold(self):
         """(weight in 32-bit, eps) for a product that folds this norm in, see
@@ -39,10 +50,18 @@ class RMSNorm(Norm):
         return self._weight32, self.eps
 
     def forward(self, ctx, x: torch.Tensor, rows: Optional[torch.Tensor] = None,
-                out_name: str = "normed") -> torch.Tensor:
+                out_name: str = "normed", stream_weights: Optional[torch.Tensor] = None) -> torch.Tensor:
         n = x.shape[0] if rows is None else rows.shape[0]
         out = ctx.ws.get(out_name, (n, self.width), self.dtype)
-        self.ops.rmsnorm(x, self.weight, self.eps, out, rows)
+        if x.dim() == 3:
+            if stream_weights is None:
+                S = x.shape[1]
+                if S not in self._ones:
+                    self._ones[S] = torch.ones(S, dtype=torch.float32, device=x.device)
+                stream_weights = self._ones[S]
+            self.ops.streams_rmsnorm(x, stream_weights, self.weight, self.eps, out, rows)
+        else:
+            self.ops.rmsnorm(x, self.weight, self.eps, out, rows)
         return out
 
 

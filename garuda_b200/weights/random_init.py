@@ -50,7 +50,7 @@ def random_weights(config_dict: dict, seed: int, norm_init=None, store_dtype=tor
     out = {}
     for name, ts in model.expected_tensors().items():
         init = tuple(norm_init) if (norm_init is not None and ts.role == "vector") else ts.init
-        t = random_tensor(seed, name, ts.shape, init)
+        t = random_tensor(seed, name, ts.concrete(), init)
         for key, factor in (scale or {}).items():
             if key in name:
                 t = t * float(factor)

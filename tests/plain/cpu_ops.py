@@ -27,7 +27,14 @@ class CpuOps:
 
     # garuda/src/llama/mod.rs:198-200, :1078-1085
     def embedding(self, table, ids, out, scale=1.0):
-        out[: ids.shape[0]] = table[ids.long()].float() * scale
+        rows = table[ids.long()].float() * scale
+        out[: ids.shape[0]] = rows[:, None, :] if out.dim() == 3 else rows
+
+    def scale_softcap(self, x, scale=1.0, cap=0.0):
+        """x * scale, then cap * tanh(x / cap)"""
+        x *= scale
+        if cap > 0:
+            x.copy_(cap * torch.tanh(x / cap))
 
     # garuda/src/simd/mod.rs:166-173; garuda/src/llama/mod.rs:733-738
     def rmsnorm(self, x, weight, eps, out, rows=None):
@@ -120,11 +127,13 @@ class CpuOps:
     # garuda/src/llama/mod.rs:793-818; garuda/src/cache/mod.rs:333-338
     def paged_attention(self, q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out,
                         scale, window, page_size, num_requests, max_q_len, max_kv_len, ws=None, min_q_len=1,
-                        value_dim=None):
+                        value_dim=None, softcap=0.0, keep_first=0, sink=False):
+        """softcap c: s <- c tanh(s / c); keep_first n: a windowed query also reads positions below n;
+        sink: p_j = exp(s_j) / (1 + sum exp(s_k))"""
         T, Hq, hd = q.shape
         Hkv = k_pool.shape[1]
         g = Hq // Hkv
-        vd = hd if value_dim is None else value_dim
+        vd = v_pool.shape[3] if value_dim is None else value_dim
         res = torch.zeros(T, Hq, vd)
         for t in range(T):
             r = int(token_req[t])
@@ -132,13 +141,20 @@ class CpuOps:
             pos = int(kv_lens[r]) - q_len + (t - int(cu_q[r]))
             start = max(0, pos + 1 - window) if window else 0
             js = torch.arange(start, pos + 1)
+            if window and keep_first and start > 0:
+                js = torch.cat([torch.arange(0, min(keep_first, start)), js])
             pages = block_table[r, (js // page_size)].long()
             assert (pages >= 0).all(), "attention reads a position whose page was given back"
             K = k_pool[pages, :, (js % page_size), :].float()    # [n, Hkv, hd]
             V = v_pool[pages, :, (js % page_size), :vd].float()
             for h in range(Hq):
                 s = (K[:, h // g, :] @ q[t, h].float()) * scale
-                p = torch.softmax(s, 0)
+                if softcap:
+                    s = softcap * torch.tanh(s / softcap)
+                if sink:
+                    p = torch.softmax(torch.cat([s, torch.zeros(1)]), 0)[:-1]
+                else:
+                    p = torch.softmax(s, 0)
                 res[t, h] = p @ V[:, h // g, :]
         out.copy_(res.reshape(T, Hq * vd).to(out.dtype))
 
@@ -190,20 +206,22 @@ class CpuOps:
     def linear_gated(self, ctx, h, w_gate_up, act, kind="silu", limit=0.0):
         self.gated_act(h.float() @ w_gate_up.float().t(), act, kind, limit)
 
-    def route_topk(self, h, w_router, bias, top, ids, weights):
+    def route_topk(self, h, w_router, bias, top, ids, weights, score="softmax_chosen"):
         z = h.float() @ w_router.float().t()
         if bias is not None:
             z = z + bias.float()
         order = torch.sort(-z, dim=-1, stable=True).indices[:, :top]
         ids.copy_(order.to(torch.int32))
-        weights.copy_(torch.softmax(torch.gather(z, 1, order), -1))
+        chosen = torch.gather(z, 1, order)
+        weights.copy_(torch.sigmoid(chosen) if score == "sigmoid" else torch.softmax(chosen, -1))
 
-    def moe_gate_up(self, h, w_gate_up, ids, act, kind, limit):
+    def moe_gate_up(self, h, w_gate_up, ids, act, kind, limit, in_scale=None):
         T, top = ids.shape
         F = act.shape[2]
         for t in range(T):
             for j in range(top):
-                gu = (w_gate_up[int(ids[t, j])].float() @ h[t].float())[None, :]
+                x = h[t].float() * (float(in_scale[t, j]) if in_scale is not None else 1.0)
+                gu = (w_gate_up[int(ids[t, j])].float() @ x)[None, :]
                 self.gated_act(gu, act[t, j][None, :], kind, limit)
 
     def moe_down(self, act, w_down, ids, weights, x, alpha=1.0):
@@ -211,17 +229,92 @@ class CpuOps:
         for t in range(T):
             total = torch.zeros(x.shape[1])
             for j in range(top):
-                total += weights[t, j] * (w_down[int(ids[t, j])].float() @ act[t, j].float())
+                wt = weights[t, j] if weights is not None else 1.0
+                total += wt * (w_down[int(ids[t, j])].float() @ act[t, j].float())
             x[t] += alpha * total
 
     def pack_expert_gate_up(self, gates, ups):
         return torch.stack([torch.cat([g, u], 0) for g, u in zip(gates, ups)]).contiguous()
 
-    def routed_feed_forward(self, ctx, h, w_gate_up, w_down, ids, weights, x, kind, limit, alpha=1.0):
+    def routed_feed_forward(self, ctx, h, w_gate_up, w_down, ids, weights, x, kind, limit, alpha=1.0, scale_input=False):
         T, top = ids.shape
         act = torch.zeros(T, top, w_down.shape[2], dtype=h.dtype)
-        self.moe_gate_up(h, w_gate_up, ids, act, kind, limit)
-        self.moe_down(act, w_down, ids, weights, x, alpha)
+        self.moe_gate_up(h, w_gate_up, ids, act, kind, limit, weights if scale_input else None)
+        self.moe_down(act, w_down, ids, None if scale_input else weights, x, alpha)
+
+    # ---- a residual of several streams ----
+    def streams_rmsnorm(self, x, in_w, weight, eps, out, rows=None):
+        """rms(sum_s in_w[s] x[:, s]) * weight"""
+        xs = x if rows is None else x[rows.long()]
+        u = torch.einsum("s,tsd->td", in_w.float(), xs)
+        out.copy_((u / torch.sqrt((u * u).mean(-1, keepdim=True) + eps) * weight.float()).to(out.dtype))
+
+    def streams_update(self, x, mix, out_w, y, next_in=None, norm_weight=None, eps=0.0, normed=None):
+        """x[:, j] <- sum_s mix[s, j] x[:, s] + out_w[j] y, all j from the old streams"""
+        S = x.shape[1]
+        new = torch.einsum("sj,tsd->tjd", mix.float().reshape(S, S), x) + out_w.float()[None, :, None] * y[:, None, :]
+        x.copy_(new)
+        if next_in is not None:
+            self.streams_rmsnorm(x, next_in, norm_weight, eps, normed)
+
+    def qkv_bias_append(self, qkv, bias, q_out, k_pool, v_pool, positions, token_req, block_table, heads, kv_heads,
+                        head_dim, value_dim, page_size):
+        T = qkv.shape[0]
+        x = qkv.float() + (bias.float() if bias is not None else 0.0)
+        nq, nk = heads * head_dim, kv_heads * head_dim
+        q_out.copy_(x[:, :nq].reshape(T, heads, head_dim).to(q_out.dtype))
+        k = x[:, nq:nq + nk].reshape(T, kv_heads, head_dim)
+        v = x[:, nq + nk:].reshape(T, kv_heads, value_dim)
+        for t in range(T):
+            pos = int(positions[t])
+            page = int(block_table[int(token_req[t]), pos // page_size])
+            if page >= 0:
+                k_pool[page, :, pos % page_size, :] = k[t].to(k_pool.dtype)
+                v_pool[page, :, pos % page_size, :] = v[t].to(v_pool.dtype)
+
+    # ---- the gated delta rule with a decay per key channel ----
+    def delta_rule(self, ctx, proj, second, conv_w, a_log, dt_bias, norm_w, eps, state, heads, kv_heads, dim, vdim,
+                   taps, out):
+        """Per request, token by token: the convolution over the kept last inputs and the new one,
+        SiLU, unit vectors, S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q; then
+        o / rms(o) * norm_w * sigmoid(gate)."""
+        b = ctx.batch
+        H, G = heads, kv_heads
+        C = 2 * G * dim + H * vdim
+        n_state = H * dim * vdim
+        cu, slots = b.cu_q.tolist(), b.slots.tolist()
+        cw = conv_w.float()
+        rate = torch.exp(a_log.float())
+        for r, slot in enumerate(slots):
+            if slot < 0:
+                out[cu[r]:cu[r + 1]] = 0
+                continue
+            S = state[slot, :n_state].reshape(H, dim, vdim).clone()
+            kept = state[slot, n_state:].reshape(taps - 1, C).clone()
+            for t in range(cu[r], cu[r + 1]):
+                x = proj[t, :C]
+                window = torch.cat([kept, x[None, :]], 0)                   # [taps, C], oldest first
+                a = (window * cw.t()).sum(0)
+                a = a / (1.0 + torch.exp(-a))
+                kept = window[1:]
+                q = a[:G * dim].reshape(G, dim)
+                k = a[G * dim:2 * G * dim].reshape(G, dim)
+                v = a[2 * G * dim:].reshape(H, vdim)
+                q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * dim ** -0.5
+                k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+                beta = torch.sigmoid(proj[t, C:C + H])
+                g = torch.exp(-rate[:, None] * torch.nn.functional.softplus(second[t, :H * dim] + dt_bias.float()).reshape(H, dim))
+                gate = torch.sigmoid(second[t, H * dim:]).reshape(H, vdim)
+                for n in range(H):
+                    kk, qq = k[n // (H // G)], q[n // (H // G)]
+                    S[n] = g[n][:, None] * S[n]
+                    u = beta[n] * (v[n] - S[n].t() @ kk)
+                    S[n] = S[n] + kk[:, None] * u[None, :]
+                    o = S[n].t() @ qq
+                    o = o / torch.sqrt((o * o).mean() + eps) * norm_w.float() * gate[n]
+                    out[t, n * vdim:(n + 1) * vdim] = o.to(out.dtype)
+            state[slot, :n_state] = S.reshape(-1)
+            state[slot, n_state:] = kept.reshape(-1)
 
     def latent_append(self, src, norm_w, eps, rank, rot, rotary, positions, token_req, block_table, pool, page_size):
         """rows [rms(src[:, :rank]) * w | rotate(src[:, rank:])] into their pages"""
