@@ -5,6 +5,7 @@
 
     python bench.py --shape tinyllama|llama2-7b|llama3-8b [--layers L]
 
+    python bench.py --design murilorn [--size 2k,4k]    (likewise for the third architecture)
     python bench.py --design kavenex [--size 2k,4k]     (a JSON line of its own: the second architecture
                                                          beside Llama at equal sizes, kernel beside like kernel)
 
@@ -646,6 +647,214 @@ def run_one_phase(args, engine, cfg, rng, context) -> dict:
             "ms": [round(t, 4) for t in times]}
 
 
+# ``--design murilorn``: the Murilorn design beside the Llama decoder at equal width, heads, head size and
+# depth (random weights). Four layers: three delta-rule layers and one of windowed attention, each with
+# routed experts (a token's `top` experts together as large as Llama's feed-forward), two streams.
+MURILORN_SIZES = {
+    "2k": dict(width=2048, heads=32, kv_heads=4, dim=64, window=1024, keep_first=4, softcap=30.0, d_heads=16, d_kv_heads=16,
+               d_dim=128, d_vdim=128, taps=4, rank=64, experts=16, top=4, expert_ff=1408, streams=2, vocab=32000),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, window=1024, keep_first=4, softcap=30.0, d_heads=32, d_kv_heads=16,
+               d_dim=128, d_vdim=128, taps=4, rank=128, experts=16, top=4, expert_ff=2752, streams=2, vocab=32000),
+}
+
+
+def murilorn_configs(z):
+    attn = {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                                           "scale": z["dim"] ** -0.5, "softcap": z["softcap"],
+                                           "mask": {"size": z["window"], "keep_first": z["keep_first"]}}}
+    delta = {"type": "channel_delta", "mixer": {"heads": z["d_heads"], "kv_heads": z["d_kv_heads"], "dim": z["d_dim"],
+                                                "vdim": z["d_vdim"], "conv": z["taps"], "decay_rank": z["rank"], "gate_rank": z["rank"]}}
+    moe = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["expert_ff"]}}
+    murilorn = {"architecture": "Murilorn", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 1.0},
+                "norm": {"eps": 1e-5}, "streams": z["streams"], "logit_scale": 1.0, "logit_softcap": 30.0, "max_positions": 4096,
+                "layers": [dict(m, mlp=moe) for m in (delta, delta, delta, attn)]}
+    llama = dict(LLAMA, hidden_size=z["width"], num_hidden_layers=4, num_attention_heads=z["heads"],
+                 num_key_value_heads=z["kv_heads"], head_dim=z["dim"], intermediate_size=z["top"] * z["expert_ff"],
+                 vocab_size=z["vocab"], rope_theta=10000.0, max_position_embeddings=4096)
+    return murilorn, llama
+
+
+def run_design_murilorn(args) -> dict:
+    """Prefill and decode throughput of the Murilorn design and of the Llama decoder at equal sizes, and
+    the design's kernels beside the like kernels of Llama, each against its roofline (the slower of
+    bytes / measured copy rate and FLOPs / measured bfloat16 rate)."""
+    import numpy as np
+    import torch
+    from garuda_b200 import Engine, StepEntry
+    from garuda_b200.engine.batch import Workspace
+    from garuda_b200.weights import write_random_model
+
+    hbm_peak, tflops_peak, peak_kind = peaks()
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    dev = torch.device("cuda:0")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        times = []
+        for _ in range(reps):
+            flush.zero_()
+            s, e = ev(), ev()
+            torch.cuda.synchronize()
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            times.append(s.elapsed_time(e))
+        return sorted(times)[len(times) // 2]
+
+    def roof(ms, flops=0.0, nbytes=0.0):
+        ideal = max(flops / (tflops_peak * 1e12), nbytes / (hbm_peak * 1e9)) * 1e3
+        return {"ms": round(ms, 4), "roofline_ms": round(ideal, 4), "frac": round(ideal / ms, 4)}
+
+    out = {"design": "murilorn", "peaks": peak_kind, "hbm_gbs": hbm_peak, "bf16_tflops": tflops_peak, "dtype": "bf16",
+           "data": "synthetic", "timing": "CUDA events, 3 warm-up runs, L2 flushed before every timed run, median", "sizes": {}}
+    B, CTX, T = 8, 2048, PREFILL_TOKENS
+    for name in (args.size.split(",") if args.size else list(MURILORN_SIZES)):
+        z = MURILORN_SIZES[name]
+        rec, engines = {}, {}
+        for arch, cfg in zip(("murilorn", "llama"), murilorn_configs(z)):
+            tmp = tempfile.mkdtemp(prefix="garuda_bench_", dir="/dev/shm" if os.path.isdir("/dev/shm") else None)
+            try:
+                write_random_model(tmp, cfg, seed=0, store_dtype=torch.bfloat16)
+                engine = Engine(tmp, dtype="bfloat16", context=4096, page_size=32, kv_tokens=B * CTX + 4096 + 64,
+                                max_concurrent=B, max_batch_tokens=T, prefill_chunk=T, ignore_eos=True)
+            finally:
+                shutil.rmtree(tmp, ignore_errors=True)
+            engines[arch] = engine
+            runner, rng, V = engine.runner, np.random.default_rng(0), z["vocab"]
+            toks = rng.integers(0, V, T).tolist()
+            rid = [0]
+
+            def prefill():
+                rid[0] += 1
+                runner.run([StepEntry(10_000 + rid[0], toks, [T - 1])])
+                runner.end(10_000 + rid[0])
+
+            ms = timed(prefill, reps=5)
+            rec[arch] = {"prefill_2048_ms": round(ms, 3), "prefill_tok_s": round(T / ms * 1e3)}
+            steps = 48
+            for r in range(B):
+                runner.run([StepEntry(r, rng.integers(0, V, CTX - steps - 8).tolist(), [])])
+            feed = rng.integers(0, V, (steps + 8, B))
+            for i in range(8):
+                runner.run([StepEntry(r, [int(feed[i, r])], [0]) for r in range(B)])
+            marks = [ev() for _ in range(steps + 1)]
+            torch.cuda.synchronize()
+            marks[0].record()
+            for i in range(steps):
+                runner.run([StepEntry(r, [int(feed[8 + i, r])], [0]) for r in range(B)])
+                marks[i + 1].record()
+            torch.cuda.synchronize()
+            each = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(steps))
+            for r in range(B):
+                runner.end(r)
+            rec[arch].update({"decode_b8_ctx2048_ms": round(each[len(each) // 2], 4),
+                              "decode_tok_s": round(B / each[len(each) // 2] * 1e3),
+                              "graph_replays": runner.graphs.replays,
+                              "kernels_per_decode_step": runner.graphs.launches_replayed(B)})
+            if engine.ops.tc is not None:
+                engine.ops.tc.check_errors()
+        # ------------------------------------------------------------ kernel beside like kernel
+        ops = engines["murilorn"].ops
+        bf = torch.bfloat16
+        H, Hkv, hd, W, ps, win = z["heads"], z["kv_heads"], z["dim"], z["width"], 32, z["window"]
+        ws = Workspace(dev)
+
+        class Ctx:
+            pass
+        ctx = Ctx()
+        ctx.ws = ws
+        ctx.step_cache = {}
+        kern = {}
+        for label, nreq, q_len, kv_len in (("prefill_2048", 1, T, T), ("decode_b8_ctx2048", B, 1, CTX)):
+            pages = (kv_len + ps - 1) // ps
+            bt = torch.arange(nreq * pages, dtype=torch.int32, device=dev).view(nreq, pages)
+            cu = torch.arange(nreq + 1, dtype=torch.int32, device=dev) * q_len
+            kvl = torch.full((nreq,), kv_len, dtype=torch.int32, device=dev)
+            req = torch.arange(nreq, dtype=torch.int32, device=dev).repeat_interleave(q_len)
+            q = torch.randn(nreq * q_len, H, hd, device=dev).to(bf)
+            kp, vp = (torch.randn(nreq * pages, Hkv, ps, hd, device=dev).to(bf) for _ in range(2))
+            o = torch.empty(nreq * q_len, H * hd, dtype=bf, device=dev)
+            # keys a query reads: its window (and the kept first positions)
+            keys = nreq * sum(min(p + 1, win) + (z["keep_first"] if p + 1 > win else 0) for p in range(kv_len - q_len, kv_len))
+            read = nreq * min(kv_len, win + q_len)
+            ms = timed(lambda: ops.paged_attention(q, kp, vp, bt, cu, kvl, req, o, hd ** -0.5, win, ps, nreq, q_len, kv_len, ws=ws,
+                                                   min_q_len=q_len, softcap=z["softcap"], keep_first=z["keep_first"], sink=True))
+            kern[f"capped_sink_attention_{label}"] = roof(ms, 4.0 * H * hd * keys, 2.0 * (2 * read * Hkv * hd + q.numel() + o.numel()))
+            ms = timed(lambda: ops.paged_attention(q, kp, vp, bt, cu, kvl, req, o, hd ** -0.5, win, ps, nreq, q_len, kv_len, ws=ws,
+                                                   min_q_len=q_len))
+            kern[f"llama_windowed_attention_{label}"] = roof(ms, 4.0 * H * hd * keys, 2.0 * (2 * read * Hkv * hd + q.numel() + o.numel()))
+        E, top, F = z["experts"], z["top"], z["expert_ff"]
+        for label, M in (("2048_tokens", T), ("8_tokens", B)):
+            h = torch.randn(M, W, device=dev).to(bf)
+            x = torch.zeros(M, W, device=dev)
+            wgu = ops.pack_expert_gate_up([(torch.randn(F, W, device=dev) * 0.02).to(bf) for _ in range(E)],
+                                          [(torch.randn(F, W, device=dev) * 0.02).to(bf) for _ in range(E)])
+            wd = (torch.randn(E, W, F, device=dev) * 0.02).to(bf)
+            wr = (torch.randn(E, W, device=dev) * 0.5).to(bf)
+            ids = torch.empty(M, top, dtype=torch.int32, device=dev)
+            wt = torch.empty(M, top, device=dev)
+
+            def routed():
+                ops.route_topk(h, wr, None, top, ids, wt, score="sigmoid")
+                ops.routed_feed_forward(ctx, h, wgu, wd, ids, wt, x, "silu", 0.0, 1.0, scale_input=True)
+
+            used = min(E, M * top)
+            kern[f"routed_experts_{label}"] = roof(timed(routed), 2.0 * M * top * 3 * F * W, 2.0 * used * 3 * F * W)
+            FF = top * F
+            g = ops.pack_gate_up((torch.randn(FF, W, device=dev) * 0.02).to(bf), (torch.randn(FF, W, device=dev) * 0.02).to(bf))
+            dwn = (torch.randn(W, FF, device=dev) * 0.02).to(bf)
+            act = torch.empty(M, FF, dtype=bf, device=dev)
+
+            def dense():
+                ops.linear_gated(ctx, h, g, act, "silu", 0.0)
+                ops.linear(act, dwn, x, accumulate=True)
+
+            kern[f"llama_silu_feed_forward_{label}"] = roof(timed(dense), 2.0 * M * 3 * FF * W, 2.0 * 3 * FF * W)
+            del wgu, wd, g, dwn
+        # the recurrent mixer's own kernels (no counterpart in Llama): bytes are its rows in and out and the state
+        dH, dG, dd, dv, taps = z["d_heads"], z["d_kv_heads"], z["d_dim"], z["d_vdim"], z["taps"]
+        C = 2 * dG * dd + dH * dv
+        conv_w, a_log = torch.randn(C, taps, device=dev) * 0.3, torch.randn(dH, device=dev) * 0.3
+        dtb, nw = torch.randn(dH * dd, device=dev), torch.ones(dv, device=dev)
+        state = torch.zeros(B, dH * dd * dv + (taps - 1) * C, device=dev)
+
+        class Bt:
+            pass
+        for label, nreq, q_len in (("prefill_2048", 1, T), ("decode_b8", B, 1)):
+            b = Bt()
+            b.cu_q = torch.arange(nreq + 1, dtype=torch.int32, device=dev) * q_len
+            b.slots = torch.arange(nreq, dtype=torch.int32, device=dev)
+            b.token_req = torch.arange(nreq, dtype=torch.int32, device=dev).repeat_interleave(q_len)
+            b.num_requests, b.max_q_len = nreq, q_len
+            ctx.batch = b
+            n = nreq * q_len
+            proj, second = torch.randn(n, C + dH, device=dev), torch.randn(n, dH * dd + dH * dv, device=dev)
+            o = torch.empty(n, dH * dv, dtype=bf, device=dev)
+            ms = timed(lambda: ops.delta_rule(ctx, proj, second, conv_w, a_log, dtb, nw, 1e-5, state, dH, dG, dd, dv, taps, o))
+            moved = 4.0 * (proj.numel() + second.numel()) + 2.0 * o.numel() + 2 * 4.0 * nreq * state.shape[1]
+            kern[f"delta_rule_{label}"] = roof(ms, 0, moved)
+        S = z["streams"]
+        xs, y = torch.randn(T, S, W, device=dev), torch.randn(T, W, device=dev)
+        a_in, b_out, mix = torch.ones(S, device=dev), torch.ones(S, device=dev), torch.eye(S, device=dev).contiguous()
+        wv = torch.ones(W, device=dev)
+        on = torch.empty(T, W, dtype=bf, device=dev)
+        kern["streams_read_2048_tokens"] = roof(timed(lambda: ops.streams_rmsnorm(xs, a_in, wv, 1e-5, on)), 0, (4.0 * S + 2.0) * T * W)
+        kern["streams_write_and_read_2048_tokens"] = roof(
+            timed(lambda: ops.streams_update(xs, mix, b_out, y, next_in=a_in, norm_weight=wv, eps=1e-5, normed=on)), 0,
+            (8.0 * S + 4.0 + 2.0) * T * W)
+        xr = torch.randn(T, W, device=dev)
+        kern["llama_rms_norm_2048_tokens"] = roof(timed(lambda: ops.rmsnorm(xr, wv, 1e-5, on)), 0, 6.0 * T * W)
+        rec["kernels"] = kern
+        rec["config"] = {k: v for k, v in z.items()}
+        out["sizes"][name] = rec
+        del engines
+        torch.cuda.empty_cache()
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -660,7 +869,7 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=0, help="context reached with --only decode (default: the shape's); keys with --only attention")
     ap.add_argument("--layers", type=int, default=0,
                     help="fewer layers than the configuration has (reported beside the full number)")
-    ap.add_argument("--design", choices=["kavenex"],
+    ap.add_argument("--design", choices=["kavenex", "murilorn"],
                     help="instead of the default workload: this design beside the Llama decoder at equal sizes")
     ap.add_argument("--size", default="", help="with --design: which of its sizes (2k, 4k; default both)")
     args = ap.parse_args()
@@ -678,7 +887,7 @@ def main() -> int:
         print("bench.py: --batch must be 1 to 64")
         return 2
     if args.design:
-        print(json.dumps(run_design(args)))
+        print(json.dumps(run_design_murilorn(args) if args.design == "murilorn" else run_design(args)))
         return 0
     print(json.dumps(run_ours(args)))
     return 0

@@ -148,7 +148,16 @@ def latent_attention_lib_name(rank: int, rot: int) -> str:
     return f"garuda_latent_r{int(rank)}_t{int(rot)}"
 
 
+def capped_attention_lib_name(key_dim: int, value_dim: int) -> str:
+    """The tensor-core attention with capped scores, kept first positions and a sink is compiled per
+    (key width, value width), when a model first needs it."""
+    return f"garuda_cattn_k{int(key_dim)}_v{int(value_dim)}"
+
+
 def _lib_recipe(name: str):
+    if name.startswith("garuda_cattn_k"):
+        kd, vd = name[len("garuda_cattn_k"):].split("_v")
+        return ["attention_capped_mma.cu"], [f"-DGB_KEY_DIM={int(kd)}", f"-DGB_VALUE_DIM={int(vd)}"]
     if name.startswith("garuda_latent_r"):
         rank, rot = name[len("garuda_latent_r"):].split("_t")
         return ["latent_attention_mma.cu"], [f"-DGB_LATENT_RANK={int(rank)}", f"-DGB_LATENT_ROT={int(rot)}"]
@@ -259,7 +268,7 @@ def load_host_module():
     return _HOST
 
 
-def build_all(head_dims=(16, 32, 48, 64, 128), latent_sizes=((64, 32), (512, 64))) -> None:
+def build_all(head_dims=(16, 32, 48, 64, 128), latent_sizes=((64, 32), (512, 64)), capped_sizes=((64, 64), (32, 48))) -> None:
     """Everything, for a build check."""
     host_module_path()
     for name in KERNEL_LIBS:
@@ -268,3 +277,5 @@ def build_all(head_dims=(16, 32, 48, 64, 128), latent_sizes=((64, 32), (512, 64)
         kernel_lib_path(attention_lib_name(hd))
     for rank, rot in latent_sizes:
         kernel_lib_path(latent_attention_lib_name(rank, rot))
+    for kd, vd in capped_sizes:
+        kernel_lib_path(capped_attention_lib_name(kd, vd))

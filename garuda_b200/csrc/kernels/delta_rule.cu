@@ -9,10 +9,11 @@
 //   delta_prepare     a block per token: convolution over the step's rows and the request's kept
 //                     last inputs, SiLU, unit vectors, decays, beta
 //   delta_conv_state  a request's kept last inputs after the step
-//   delta_recurrence  a thread per column of S (its dim entries in registers): the columns of S are
-//                     independent of one another, so a request's tokens are walked in order with
-//                     no exchange between threads; the step's q, k and g rows come through shared
-//                     memory a few tokens at a time
+//   delta_recurrence  the columns of S are independent of one another, so a request's tokens are
+//                     walked in order with no exchange between columns: eight threads share a
+//                     column (every eighth row each, in registers) and exchange two sums per token
+//                     by shuffles; the step's q, k and g rows come through shared memory a few
+//                     tokens at a time
 //   delta_out         per head: o / rms(o) * weight * sigmoid(gate)
 //   delta_decode      all of the above for steps of one token per request, one block per
 //                     (request, head)
@@ -110,68 +111,132 @@ delta_conv_state_kernel(const float* __restrict__ proj, int P, float* __restrict
 }
 
 constexpr int CHUNK = 8;
+constexpr int SPLIT = 8;        // threads that share a column of S: thread `sub` holds the rows d with d % 8 == sub
+constexpr int REC_THREADS = 128, REC_COLS = REC_THREADS / SPLIT;
 
-// grid (H, R, ceil(vdim / blockDim.x)); a thread per column of S.
-template <int MAXD>
-__global__ void __launch_bounds__(128)
+__device__ __forceinline__ void cp_async_4(float* smem, const float* gmem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(gmem) : "memory");
+}
+
+// grid (H, R, ceil(vdim / 16)), 128 threads: 16 columns of S, eight threads a column. Each of the
+// eight sums its rows in ascending order and the eight are added as a tree, ((0 + 1) + (2 + 3)) +
+// ((4 + 5) + (6 + 7)): the same sums, in the same order, as the eight interleaved partial sums of
+// the one-token kernel below. Everything a token needs (q^, k^, g, the block's values, beta)
+// comes through shared memory, eight tokens at a time in two buffers: the next eight are on their
+// way while these are walked. EXACT: dim == MAXD, no row of a thread is beyond the head's.
+template <int MAXD, bool EXACT>
+__global__ void __launch_bounds__(REC_THREADS)
 delta_recurrence_kernel(const float* __restrict__ prep, int W, const int32_t* __restrict__ cu_q,
                         const int32_t* __restrict__ slots, float* __restrict__ state, long long state_stride, int H,
                         int G, int dim, int vdim, float* __restrict__ out) {
   gb::pdl_launch_dependents();
   gb::pdl_wait();
-  extern __shared__ float stage[];      // [CHUNK][3][dim]: q^, k^, g of a few tokens
+  constexpr int MINE = MAXD / SPLIT;
+  extern __shared__ __align__(16) float stage[];      // 2 x [CHUNK][3 SPLIT per + 32 + 4]
+  // a thread's rows, rounded up to whole 16-byte pieces, and one piece more: the four slices start
+  // in different banks and are read four values at a time
+  const int per = ((dim + SPLIT - 1) / SPLIT + 3) / 4 * 4 + 4;
+  const int tok_floats = 3 * SPLIT * per + REC_COLS + 4;      // a multiple of four: every slice starts on 16 bytes
   const int h = blockIdx.x, r = blockIdx.y;
-  const int col = blockIdx.z * blockDim.x + threadIdx.x;
+  const int sub = threadIdx.x % SPLIT;
+  const int col0 = blockIdx.z * REC_COLS, mycol = threadIdx.x / SPLIT, col = col0 + mycol;
   const bool active = col < vdim;
   const int slot = slots[r];
   const int t0 = cu_q[r], t1 = cu_q[r + 1];
   const int kvh = h / (H / G);
-  const int off_q = kvh * dim, off_k = G * dim + kvh * dim, off_v = 2 * G * dim + h * vdim + col;
+  const int off_q = kvh * dim, off_k = G * dim + kvh * dim, off_v = 2 * G * dim + h * vdim + col0;
   const int off_g = 2 * G * dim + H * vdim + h * dim, off_b = off_g - h * dim + H * dim + h;
-  float* S_g = slot >= 0 ? state + (size_t)slot * state_stride + (size_t)h * dim * vdim + col : nullptr;
-  float S[MAXD];
+  const int ncols = min(REC_COLS, vdim - col0);
+  float* S_g = (slot >= 0 && active) ? state + (size_t)slot * state_stride + (size_t)h * dim * vdim + col : nullptr;
+  float S[MINE];
 #pragma unroll
-  for (int d = 0; d < MAXD; ++d) S[d] = (d < dim && active && S_g != nullptr) ? S_g[(size_t)d * vdim] : 0.f;
-  for (int c0 = t0; c0 < t1; c0 += CHUNK) {
+  for (int i = 0; i < MINE; ++i) {
+    const int d = i * SPLIT + sub;
+    S[i] = (d < dim && S_g != nullptr) ? S_g[(size_t)d * vdim] : 0.f;
+  }
+  auto fetch = [&](int c0, int buf) {
     const int n = min(CHUNK, t1 - c0);
-    __syncthreads();
-    for (int i = threadIdx.x; i < n * dim; i += blockDim.x) {
+    float* dst = stage + (size_t)buf * CHUNK * tok_floats;
+    for (int i = threadIdx.x; i < n * dim; i += REC_THREADS) {
       const int tt = i / dim, d = i % dim;
       const float* row = prep + (size_t)(c0 + tt) * W;
-      stage[(tt * 3 + 0) * dim + d] = row[off_q + d];
-      stage[(tt * 3 + 1) * dim + d] = row[off_k + d];
-      stage[(tt * 3 + 2) * dim + d] = row[off_g + d];
+      float* to = dst + tt * tok_floats + (d % SPLIT) * per + d / SPLIT;
+      cp_async_4(to, row + off_q + d);
+      cp_async_4(to + SPLIT * per, row + off_k + d);
+      cp_async_4(to + 2 * SPLIT * per, row + off_g + d);
+    }
+    for (int i = threadIdx.x; i < n * (ncols + 1); i += REC_THREADS) {
+      const int tt = i / (ncols + 1), c = i % (ncols + 1);
+      const float* row = prep + (size_t)(c0 + tt) * W;
+      float* to = dst + tt * tok_floats + 3 * SPLIT * per;
+      if (c < ncols) cp_async_4(to + c, row + off_v + c);
+      else cp_async_4(to + REC_COLS, row + off_b);
+    }
+  };
+  if (t0 < t1) fetch(t0, 0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  int buf = 0;
+  for (int c0 = t0; c0 < t1; c0 += CHUNK, buf ^= 1) {
+    const int n = min(CHUNK, t1 - c0);
+    if (c0 + CHUNK < t1) fetch(c0 + CHUNK, buf ^ 1);       // that buffer was read two rounds ago, behind a barrier
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();
+    const float* cur = stage + (size_t)buf * CHUNK * tok_floats;
+    for (int tt = 0; tt < n; ++tt) {
+      const float* tok = cur + tt * tok_floats;
+      const float* sq = tok + sub * per;
+      const float* sk = sq + SPLIT * per;
+      const float* sg = sk + SPLIT * per;
+      const float v = active ? tok[3 * SPLIT * per + mycol] : 0.f;
+      const float beta = tok[3 * SPLIT * per + REC_COLS];
+      float acc = 0.f;
+      float kk[MINE];
+#pragma unroll
+      for (int i4 = 0; i4 < MINE; i4 += 4) {
+        if (!EXACT && i4 * SPLIT >= dim) break;         // pieces beyond the head's rows are not in shared memory
+        const float4 g4 = *reinterpret_cast<const float4*>(sg + i4);
+        const float4 k4 = *reinterpret_cast<const float4*>(sk + i4);
+        const float gg[4] = {g4.x, g4.y, g4.z, g4.w};
+        kk[i4] = k4.x, kk[i4 + 1] = k4.y, kk[i4 + 2] = k4.z, kk[i4 + 3] = k4.w;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (EXACT || (i4 + j) * SPLIT + sub < dim) {
+            S[i4 + j] *= gg[j];
+            acc = fmaf(S[i4 + j], kk[i4 + j], acc);
+          }
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      const float u = beta * (v - acc);
+      float o = 0.f;
+#pragma unroll
+      for (int i4 = 0; i4 < MINE; i4 += 4) {
+        if (!EXACT && i4 * SPLIT >= dim) break;
+        const float4 q4 = *reinterpret_cast<const float4*>(sq + i4);
+        const float qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (EXACT || (i4 + j) * SPLIT + sub < dim) {
+            S[i4 + j] = fmaf(kk[i4 + j], u, S[i4 + j]);
+            o = fmaf(S[i4 + j], qq[j], o);
+          }
+      }
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      o += __shfl_xor_sync(0xffffffffu, o, 4);
+      if (active && sub == 0) out[(size_t)(c0 + tt) * H * vdim + h * vdim + col] = o;
     }
     __syncthreads();
-    for (int tt = 0; tt < n; ++tt) {
-      const float* row = prep + (size_t)(c0 + tt) * W;
-      const float v = active ? row[off_v] : 0.f;
-      const float beta = row[off_b];
-      const float* sq = stage + (tt * 3 + 0) * dim;
-      const float* sk = stage + (tt * 3 + 1) * dim;
-      const float* sg = stage + (tt * 3 + 2) * dim;
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int d = 0; d < MAXD; ++d)
-        if (d < dim) {
-          S[d] *= sg[d];
-          acc[d & 3] = fmaf(S[d], sk[d], acc[d & 3]);
-        }
-      const float u = beta * (v - ((acc[0] + acc[1]) + (acc[2] + acc[3])));
-      float o[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int d = 0; d < MAXD; ++d)
-        if (d < dim) {
-          S[d] = fmaf(sk[d], u, S[d]);
-          o[d & 3] = fmaf(S[d], sq[d], o[d & 3]);
-        }
-      if (active) out[(size_t)(c0 + tt) * H * vdim + h * vdim + col] = (o[0] + o[1]) + (o[2] + o[3]);
-    }
   }
-  if (active && S_g != nullptr) {
+  if (S_g != nullptr) {
 #pragma unroll
-    for (int d = 0; d < MAXD; ++d)
-      if (d < dim) S_g[(size_t)d * vdim] = S[d];
+    for (int i = 0; i < MINE; ++i) {
+      const int d = i * SPLIT + sub;
+      if (d < dim) S_g[(size_t)d * vdim] = S[i];
+    }
   }
 }
 
@@ -210,7 +275,7 @@ delta_decode_kernel(const float* __restrict__ proj, int P, const float* __restri
                     int dim, int vdim, OT* __restrict__ out) {
   gb::pdl_launch_dependents();
   gb::pdl_wait();
-  extern __shared__ float sm[];          // q^[dim], k^[dim], g[dim], scratch[32]
+  extern __shared__ float sm[];          // q^[dim], k^[dim], g[dim], scratch[32], o[vdim]
   float* sq = sm;
   float* sk = sm + dim;
   float* sg = sm + 2 * dim;
@@ -254,31 +319,34 @@ delta_decode_kernel(const float* __restrict__ proj, int P, const float* __restri
     const float beta = sigmoid(proj[(size_t)t * P + C + h]);
     float* S_g = slot >= 0 ? state + (size_t)slot * state_stride + (size_t)h * dim * vdim + col : nullptr;
     float S[MAXD];
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int d = 0; d < MAXD; ++d)
       if (d < dim) {
         S[d] = (S_g != nullptr ? S_g[(size_t)d * vdim] : 0.f) * sg[d];
-        acc[d & 3] = fmaf(S[d], sk[d], acc[d & 3]);
+        acc[d & 7] = fmaf(S[d], sk[d], acc[d & 7]);
       }
-    const float u = beta * (v - ((acc[0] + acc[1]) + (acc[2] + acc[3])));
-    float o[4] = {0.f, 0.f, 0.f, 0.f};
+    // the tree the kernel for longer steps adds its eight threads' sums by
+    const float u = beta * (v - (((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]))));
+    float o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int d = 0; d < MAXD; ++d)
       if (d < dim) {
         S[d] = fmaf(sk[d], u, S[d]);
-        o[d & 3] = fmaf(S[d], sq[d], o[d & 3]);
+        o[d & 7] = fmaf(S[d], sq[d], o[d & 7]);
         if (S_g != nullptr) S_g[(size_t)d * vdim] = S[d];
       }
-    o_val = (o[0] + o[1]) + (o[2] + o[3]);
+    o_val = ((o[0] + o[1]) + (o[2] + o[3])) + ((o[4] + o[5]) + (o[6] + o[7]));
   }
-  // the head's RMS over vdim, the weight and the output gate
-  float ss = gb::warp_sum(o_val * o_val);
-  if (lane == 0) scratch[warp] = ss;
+  // the head's RMS over vdim, the weight and the output gate; the sum of squares in the order the
+  // kernel for longer steps takes it (a lane's channels in ascending order, then the warp's tree),
+  // so that a token's result is the same bits whichever kernel ran it
+  float* so = scratch + 32;            // [vdim]
+  if (active) so[col] = o_val;
   __syncthreads();
-  float total = 0.f;
-  for (int i = 0; i < warps; ++i) total += scratch[i];
-  const float scale = 1.0f / sqrtf(total / (float)vdim + eps);
+  float ss = 0.f;
+  for (int c = lane; c < vdim; c += 32) ss = fmaf(so[c], so[c], ss);
+  const float scale = 1.0f / sqrtf(gb::warp_sum(ss) / (float)vdim + eps);
   if (active) {
     const float gate = second[(size_t)t * P2 + H * dim + h * vdim + col];
     out[((size_t)t * H + h) * vdim + col] = gb::from_float<OT>((o_val * scale) * gb::to_float<WT>(norm_w[col]) * sigmoid(gate));
@@ -338,13 +406,22 @@ GB_EXPORT int gb_delta_recurrence(const float* prep, int W, const int32_t* cu_q,
   if (R <= 0) return GB_OK;
   int rc = check_sizes("delta_recurrence", H, G, dim, vdim, 1);
   if (rc != GB_OK) return rc;
-  const int threads = vdim >= 128 ? 128 : (vdim + 31) / 32 * 32;
-  const dim3 grid(H, R, (vdim + threads - 1) / threads);
-  const size_t smem = (size_t)CHUNK * 3 * dim * sizeof(float);
+  const int threads = REC_THREADS, cols = REC_COLS;
+  const dim3 grid(H, R, (vdim + cols - 1) / cols);
+  const int per = ((dim + SPLIT - 1) / SPLIT + 3) / 4 * 4 + 4;
+  const size_t smem = (size_t)2 * CHUNK * (3 * SPLIT * per + REC_COLS + 4) * sizeof(float);
   return by_dim(dim, "delta_recurrence", [&](auto maxd) -> int {
-    return gb::check_pdl_launch(gb::launch_pdl(delta_recurrence_kernel<decltype(maxd)::value>, grid, dim3(threads), smem,
-                                               stream, dim3(1, 1, 1), prep, W, cu_q, slots, state, state_stride, H, G, dim,
-                                               vdim, out),
+    if (smem > 48 * 1024) {     // never with these tile sizes (key widths up to 256 need 34 KB); kept for larger ones
+      cudaError_t e1 = cudaFuncSetAttribute(delta_recurrence_kernel<decltype(maxd)::value, true>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      cudaError_t e2 = cudaFuncSetAttribute(delta_recurrence_kernel<decltype(maxd)::value, false>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e1 != cudaSuccess || e2 != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "delta_recurrence: shared memory");
+    }
+    constexpr int MAXD = decltype(maxd)::value;
+    auto kernel = dim == MAXD ? delta_recurrence_kernel<MAXD, true> : delta_recurrence_kernel<MAXD, false>;
+    return gb::check_pdl_launch(gb::launch_pdl(kernel, grid, dim3(threads), smem, stream, dim3(1, 1, 1), prep, W, cu_q,
+                                               slots, state, state_stride, H, G, dim, vdim, out),
                                 "delta_recurrence");
   });
 }
@@ -372,7 +449,7 @@ GB_EXPORT int gb_delta_decode(const float* proj, int P, const float* second, int
   if (rc != GB_OK) return rc;
   if (vdim > 256) return gb::fail(GB_UNSUPPORTED, "delta_decode: %d value channels per head (at most 256)", vdim);
   const int threads = (vdim + 31) / 32 * 32;
-  const size_t smem = (size_t)(3 * dim + 32) * sizeof(float);
+  const size_t smem = (size_t)(3 * dim + 32 + vdim) * sizeof(float);
   return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
     return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
       return by_dim(dim, "delta_decode", [&](auto maxd) -> int {

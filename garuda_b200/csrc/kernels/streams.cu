@@ -22,11 +22,13 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return total;
 }
 
-// out[r] = rms(sum_s in_w[s] x[row][s]) * w, row = rows ? rows[r] : r
-template <typename WT, typename OT>
+// out[r] = rms(sum_s in_w[s] x[row][s]) * w, row = rows ? rows[r] : r. NS: the number of streams
+// where it is one of the usual few (the weights then live in registers), 0: any, read at run time.
+template <int NS, typename WT, typename OT>
 __global__ void __launch_bounds__(THREADS)
 streams_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ in_w, const WT* __restrict__ w, float eps,
-                       OT* __restrict__ out, const int32_t* __restrict__ rows, int S, int d) {
+                       OT* __restrict__ out, const int32_t* __restrict__ rows, int S_any, int d) {
+  const int S = NS > 0 ? NS : S_any;
   gb::pdl_launch_dependents();
   gb::pdl_wait();
   extern __shared__ float u_s[];        // [d]
@@ -40,7 +42,9 @@ streams_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ in
   float ss = 0.f;
   for (int c = threadIdx.x; c < d; c += blockDim.x) {
     float u = 0.f;
-    for (int s = 0; s < S; ++s) u = fmaf(a_s[s], xr[(size_t)s * d + c], u);
+#pragma unroll
+    for (int s = 0; s < (NS > 0 ? NS : MAX_STREAMS); ++s)
+      if (s < S) u = fmaf(a_s[s], xr[(size_t)s * d + c], u);
     u_s[c] = u;
     ss = fmaf(u, u, ss);
   }
@@ -50,11 +54,13 @@ streams_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ in
 }
 
 // NEXT: also normed[t] = rms(sum_s next_in[s] x_s') * w
-template <bool NEXT, typename WT, typename OT>
+template <int NS, bool NEXT, typename WT, typename OT>
 __global__ void __launch_bounds__(THREADS)
 streams_update_kernel(float* __restrict__ x, const float* __restrict__ mix, const float* __restrict__ out_w,
-                      const float* __restrict__ y, int S, int d, const float* __restrict__ next_in,
+                      const float* __restrict__ y, int S_any, int d, const float* __restrict__ next_in,
                       const WT* __restrict__ w, float eps, OT* __restrict__ normed) {
+  constexpr int LIM = NS > 0 ? NS : MAX_STREAMS;
+  const int S = NS > 0 ? NS : S_any;
   gb::pdl_launch_dependents();
   gb::pdl_wait();
   extern __shared__ float u_s[];        // [d] (NEXT only)
@@ -66,24 +72,32 @@ streams_update_kernel(float* __restrict__ x, const float* __restrict__ mix, cons
     a_s[threadIdx.x] = NEXT ? next_in[threadIdx.x] : 0.f;
   }
   __syncthreads();
+  // with a known number of streams the weights are read once, into registers
+  float m_r[NS > 0 ? NS * NS : 1], b_r[NS > 0 ? NS : 1];
+  if (NS > 0) {
+#pragma unroll
+    for (int i = 0; i < NS * NS; ++i) m_r[NS > 0 ? i : 0] = m_s[i];
+#pragma unroll
+    for (int i = 0; i < NS; ++i) b_r[NS > 0 ? i : 0] = b_s[i];
+  }
   const int t = blockIdx.x;
   float* xr = x + (size_t)t * S * d;
   const float* yr = y + (size_t)t * d;
   float ss = 0.f;
   for (int c = threadIdx.x; c < d; c += blockDim.x) {
-    float old[MAX_STREAMS];
+    float old[LIM];
 #pragma unroll
-    for (int s = 0; s < MAX_STREAMS; ++s) old[s] = s < S ? xr[(size_t)s * d + c] : 0.f;
+    for (int s = 0; s < LIM; ++s) old[s] = s < S ? xr[(size_t)s * d + c] : 0.f;
     const float yv = yr[c];
     float u = 0.f;
 #pragma unroll
-    for (int to = 0; to < MAX_STREAMS; ++to) {
+    for (int to = 0; to < LIM; ++to) {
       if (to < S) {
         float v = 0.f;
 #pragma unroll
-        for (int s = 0; s < MAX_STREAMS; ++s)
-          if (s < S) v = fmaf(m_s[s * S + to], old[s], v);
-        v = fmaf(b_s[to], yv, v);
+        for (int s = 0; s < LIM; ++s)
+          if (s < S) v = fmaf(NS > 0 ? m_r[NS > 0 ? s * NS + to : 0] : m_s[s * S + to], old[s], v);
+        v = fmaf(NS > 0 ? b_r[NS > 0 ? to : 0] : b_s[to], yv, v);
         xr[(size_t)to * d + c] = v;
         if (NEXT) u = fmaf(a_s[to], v, u);
       }
@@ -145,7 +159,10 @@ GB_EXPORT int gb_streams_rmsnorm(const float* x, const float* in_w, const void* 
   if (smem > 48 * 1024) return gb::fail(GB_UNSUPPORTED, "streams_rmsnorm: width %d", d);
   return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
     return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
-      return gb::check_pdl_launch(gb::launch_pdl(streams_rmsnorm_kernel<WT, OT>, dim3(n_rows), dim3(THREADS), smem, stream,
+      auto kernel = S == 1 ? streams_rmsnorm_kernel<1, WT, OT> : S == 2 ? streams_rmsnorm_kernel<2, WT, OT>
+                  : S == 3 ? streams_rmsnorm_kernel<3, WT, OT> : S == 4 ? streams_rmsnorm_kernel<4, WT, OT>
+                  : streams_rmsnorm_kernel<0, WT, OT>;
+      return gb::check_pdl_launch(gb::launch_pdl(kernel, dim3(n_rows), dim3(THREADS), smem, stream,
                                                  dim3(1, 1, 1), x, in_w, (const WT*)w, eps, (OT*)out, rows, S, d),
                                   "streams_rmsnorm");
     });
@@ -159,8 +176,11 @@ GB_EXPORT int gb_streams_update(float* x, const float* mix, const float* out_w, 
   if (T <= 0) return GB_OK;
   if (S < 1 || S > MAX_STREAMS) return gb::fail(GB_UNSUPPORTED, "streams_update: %d streams (at most %d)", S, MAX_STREAMS);
   if (next_in == nullptr) {
+    auto kernel = S == 1 ? streams_update_kernel<1, false, float, float> : S == 2 ? streams_update_kernel<2, false, float, float>
+                : S == 3 ? streams_update_kernel<3, false, float, float> : S == 4 ? streams_update_kernel<4, false, float, float>
+                : streams_update_kernel<0, false, float, float>;
     return gb::check_pdl_launch(
-        gb::launch_pdl(streams_update_kernel<false, float, float>, dim3(T), dim3(THREADS), 0, stream, dim3(1, 1, 1), x, mix,
+        gb::launch_pdl(kernel, dim3(T), dim3(THREADS), 0, stream, dim3(1, 1, 1), x, mix,
                        out_w, y, S, d, (const float*)nullptr, (const float*)nullptr, 0.f, (float*)nullptr),
         "streams_update");
   }
@@ -168,8 +188,11 @@ GB_EXPORT int gb_streams_update(float* x, const float* mix, const float* out_w, 
   if (smem > 40 * 1024) return gb::fail(GB_UNSUPPORTED, "streams_update: width %d", d);
   return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
     return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
+      auto kernel = S == 1 ? streams_update_kernel<1, true, WT, OT> : S == 2 ? streams_update_kernel<2, true, WT, OT>
+                  : S == 3 ? streams_update_kernel<3, true, WT, OT> : S == 4 ? streams_update_kernel<4, true, WT, OT>
+                  : streams_update_kernel<0, true, WT, OT>;
       return gb::check_pdl_launch(
-          gb::launch_pdl(streams_update_kernel<true, WT, OT>, dim3(T), dim3(THREADS), smem, stream, dim3(1, 1, 1), x, mix,
+          gb::launch_pdl(kernel, dim3(T), dim3(THREADS), smem, stream, dim3(1, 1, 1), x, mix,
                          out_w, y, S, d, next_in, (const WT*)w, eps, (OT*)normed),
           "streams_update");
     });

@@ -508,7 +508,7 @@ class CudaOps:
         plain = softcap == 0.0 and keep_first == 0 and not sink and v_hd == hd
         if not plain and self.tc is not None and q.dtype == torch.bfloat16 and vd == v_hd and self.tc.capped_attention(
                 q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, scale, window, page_size,
-                num_requests, max_q_len, max_kv_len, ws, softcap, keep_first, sink):
+                num_requests, max_q_len, max_kv_len, ws, softcap, keep_first, sink, min_q_len):
             return
         if (plain and vd < hd and Hkv == 1 and window == 0 and self.tc is not None and q.dtype == torch.bfloat16
                 and k_pool.data_ptr() == v_pool.data_ptr()

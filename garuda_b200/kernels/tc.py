@@ -11,7 +11,7 @@ from ctypes import c_void_p, c_int, c_float
 
 import torch
 
-from ..csrc.build import load_kernel_lib, attention_lib_name, latent_attention_lib_name
+from ..csrc.build import load_kernel_lib, attention_lib_name, latent_attention_lib_name, capped_attention_lib_name
 
 _WAIT_NAMES = {1: "an operand tile never arrived (TMA)", 2: "a pipeline stage was never released",
                3: "the accumulator never completed", 4: "copies in flight did not land while winding down",
@@ -55,6 +55,7 @@ class TensorCoreKernels:
         L.gb_tc_hint_next_stream.restype = c_int
         self._attn = {}
         self._latent = {}
+        self._capped = {}
         # The weights that the products of a step stream, in launch order: recorded during one run
         # (``record_streams``) and replayed as hints during the next (``hint_streams``), so that every
         # few-token product asks for the weights of the product behind it to be brought into L2 while
@@ -273,10 +274,48 @@ class TensorCoreKernels:
         return True
 
     def capped_attention(self, q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, scale, window,
-                         page_size, num_requests, max_q_len, max_kv_len, ws, softcap, keep_first, sink) -> bool:
+                         page_size, num_requests, max_q_len, max_kv_len, ws, softcap, keep_first, sink, min_q_len=1) -> bool:
         """Attention with capped scores, kept first positions, a sink or values of another width
-        than the keys on the tensor cores; False where no such kernel takes the shape."""
-        return False
+        than the keys on the tensor cores; False where no such kernel takes the shape (widths that
+        are no multiple of 16 or beyond 128, groups of more than 64 heads)."""
+        T, Hq, hd = q.shape
+        Hkv, vd = k_pool.shape[1], v_pool.shape[3]
+        if hd % 16 or vd % 16 or hd > 128 or vd > 128 or Hq // Hkv > 64:
+            return False
+        lib = self._capped.get((hd, vd))
+        if lib is None:
+            lib = load_kernel_lib(capped_attention_lib_name(hd, vd))
+            lib.gb_last_error.restype = ctypes.c_char_p
+            lib.gb_capped_attention.argtypes = ([c_void_p] * 5 + [c_int] + [c_void_p] * 2 + [c_int] * 4 + [c_float, c_float]
+                                                + [c_int] * 7 + [c_void_p, ctypes.c_longlong, c_void_p])
+            lib.gb_capped_attention.restype = c_int
+            lib.gb_capped_attention_scratch_bytes.argtypes = [c_int, c_int, c_int]
+            lib.gb_capped_attention_scratch_bytes.restype = ctypes.c_longlong
+            self._capped[(hd, vd)] = lib
+        g = Hq // Hkv
+        has_decode = min_q_len * g <= 16
+        splits = self.capped_plan(num_requests, Hkv, max_kv_len, window, keep_first) if has_decode else 1
+        need = int(lib.gb_capped_attention_scratch_bytes(num_requests, Hkv, splits))
+        scratch = None
+        if need:
+            scratch = (ws if ws is not None else self.ops.private_ws).get("capped_partials", (need,), torch.uint8)
+        code = lib.gb_capped_attention(
+            q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(), block_table.data_ptr(),
+            block_table.shape[1], cu_q.data_ptr(), kv_lens.data_ptr(), T, num_requests, Hq, Hkv, float(scale),
+            float(softcap), int(window), int(keep_first), int(bool(sink)), int(page_size), int(max_q_len), int(min_q_len),
+            int(splits), None if scratch is None else scratch.data_ptr(), need, self.ops._stream())
+        self.ops._check(lib, code, "capped_attention",
+                        ((2 if splits > 1 else 1) if has_decode else 0) + (1 if max_q_len * g > 16 else 0))
+        return True
+
+    @staticmethod
+    def capped_plan(num_requests: int, kv_heads: int, max_kv_len: int, window: int, keep_first: int) -> int:
+        """CTAs that share a decode request's key tiles: enough for about two CTAs an SM, each with
+        at least two tiles of 64 keys, at most 32. The number of tiles is bounded by the window."""
+        keys = max_kv_len if window <= 0 else min(max_kv_len, window + 63 + (keep_first + 63) // 64 * 64)
+        tiles = max((keys + 63) // 64, 1)
+        pairs = max(num_requests * kv_heads, 1)
+        return max(1, min(296 // pairs, tiles // 2, 32))
 
     # ------------------------------------------------------------------ attention over cached latent rows
     @staticmethod

@@ -30,7 +30,7 @@ class TensorSpec:
     contraction or an embedding table: held in the compute dtype), ``"vector"``
     (a norm weight or the like: a tensor stored in 32-bit stays 32-bit) or
     ``"table"`` (integers: held as int32). ``init`` describes the random-weights
-    mode: ``("normal", std)``, ``("ones",)`` or ``("normal_about_one", std)``. A size that
+    mode: ``("normal", std)``, ``("ones",)``, ``("normal_about_one", std)`` or ``("normal_about_identity", std)``. A size that
     the configuration does not give (the rank of a low-rank pair of matrices) is written ``None``
     in ``shape``: the loader takes what the file has there and checks the other sizes;
     random weights use ``free`` for it."""

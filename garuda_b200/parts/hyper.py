@@ -40,7 +40,7 @@ class StreamMixing(Connection):
         S = self.streams
         return {self.in_name: TensorSpec((S,), role="vector", init=("normal_about_one", 0.2)),
                 self.out_name: TensorSpec((S,), role="vector", init=("normal_about_one", 0.2)),
-                self.mix_name: TensorSpec((S, S), role="vector", init=("normal", 0.4))}
+                self.mix_name: TensorSpec((S, S), role="vector", init=("normal_about_identity", 0.15))}
 
     def load(self, tensors, ops, dtype):
         super().load(tensors, ops, dtype)

@@ -151,3 +151,32 @@ def test_fill_block_tables():
     assert list(out[0, 0, :2]) == list(m.block_table_row(6, 0)[:2])
     assert list(out[1, 1, :3]) == list(m.block_table_row(5, 1)[:3])
     assert (out[:, :, 2:] == -1).all()
+
+
+def test_kept_first_positions_hold_their_pages_while_the_window_moves_on():
+    # pages of 4; a window of 6 that also keeps the first 5 positions: pages 0 and 1 stay for good
+    m = host.CacheManager([host.GroupConfig(8, 6, 5), host.GroupConfig(8, 6)], 4, 2, 64)
+    m.acquire(1)
+    for n in range(1, 41):
+        m.reserve(1, n)
+        m.commit(1, n)
+        m.check_invariants()
+        kept = list(m.block_table_row(1, 0))
+        plain = list(m.block_table_row(1, 1))
+        first = max(0, n + 1 - 6) // 4          # first page the next query's window touches
+        assert all(kept[p] >= 0 for p in (0, 1)[:(n + 3) // 4])
+        assert all((kept[p] >= 0) == (plain[p] >= 0) for p in range(2, len(kept)))
+        assert all(plain[p] < 0 for p in range(first))
+        assert all(kept[p] < 0 for p in range(2, first))
+    assert m.free_pages(0) == m.free_pages(1) - 2
+    m.release(1)
+    assert m.free_pages(0) == 8 and m.free_pages(1) == 8
+    # a request that arrives whole takes every page at once and gives the middle ones back
+    m.acquire(2)
+    m.reserve(2, 30)
+    assert m.free_pages(0) == 0
+    m.commit(2, 30)
+    assert [p >= 0 for p in m.block_table_row(2, 0)[:8]] == [True, True, False, False, False, False, True, True]
+    m.check_invariants()
+    with pytest.raises(host.CacheError):
+        host.CacheManager([host.GroupConfig(4, 6, -1)], 4, 2, 64)
