@@ -77,9 +77,9 @@ __device__ __forceinline__ float tanh_exp2(float x) {
 // tanh(x): within [-1, 1] (a score below its cap, the usual case) an odd polynomial of degree 13 on
 // the multiply-add units, fitted to tanh on that interval (largest error 9e-8 as evaluated in
 // 32-bit, an ulp of the values near one), which leaves the special-function unit to the softmax's
-// exponential; beyond it the exponential form.
-__device__ __forceinline__ float tanh_score(float x) {
-  const float x2 = x * x;
+// exponential; beyond it the exponential form, which a warp takes for a tile only if one of its
+// scores is there (one test per tile, not per score).
+__device__ __forceinline__ float tanh_poly(float x, float x2) {
   float q = 0.0009637729963287711f;
   q = fmaf(q, x2, -0.005951283033937216f);
   q = fmaf(q, x2, 0.019973287358880043f);
@@ -87,9 +87,7 @@ __device__ __forceinline__ float tanh_score(float x) {
   q = fmaf(q, x2, 0.13319583237171173f);
   q = fmaf(q, x2, -0.33332130312919617f);
   q = fmaf(q, x2, 0.9999997019767761f);
-  float t = q * x;
-  if (x2 > 1.0f) t = tanh_exp2(x);
-  return t;
+  return q * x;
 }
 
 // The CTA copies keys [tile_start, tile_start + 64) of one kv head, keys and values, 16 bytes per
@@ -153,19 +151,47 @@ __device__ __forceinline__ void process(State& st, const uint32_t (&qf)[HD / 16]
   float m_new[2] = {st.m[0], st.m[1]};
   const bool capped = p.softcap > 0.f;
   const float pre = capped ? p.scale / p.softcap : p.scale, post = capped ? p.softcap : 1.0f;
+  if (capped) {
+    float largest = 0.f;
+#pragma unroll
+    for (int n = 0; n < KEYS / 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) largest = fmaxf(largest, fabsf(s[n][e]));
+    if (__any_sync(0xffffffffu, largest * pre > 1.0f)) {       // rare: a score beyond its cap
+#pragma unroll
+      for (int n = 0; n < KEYS / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float v = s[n][e] * pre, v2 = v * v;
+          s[n][e] = post * (v2 > 1.0f ? tanh_exp2(v) : tanh_poly(v, v2));
+        }
+    } else {
+#pragma unroll
+      for (int n = 0; n < KEYS / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float v = s[n][e] * pre;
+          s[n][e] = post * tanh_poly(v, v * v);
+        }
+    }
+  } else {
+#pragma unroll
+    for (int n = 0; n < KEYS / 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[n][e] *= pre;
+  }
 #pragma unroll
   for (int n = 0; n < KEYS / 8; ++n)
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int i = e >> 1;
-      float v = s[n][e] * pre;
-      if (capped) v = post * tanh_score(v);
+      float v = s[n][e];
       if (MASKED) {
         const int j = key0 + key_off + n * 8 + (lane % 4) * 2 + (e & 1);
         const bool seen = j <= row_pos[i] && (j >= row_start[i] || j < p.keep_first);
         v = seen ? v : -INFINITY;
+        s[n][e] = v;
       }
-      s[n][e] = v;
       m_new[i] = fmaxf(m_new[i], v);
     }
 #pragma unroll

@@ -29,6 +29,9 @@ from .block import BlockSpec
 @register_connection("stream_mixing")
 class StreamMixing(Connection):
     graph_safe = True
+    #: the widest row whose weighted sum the fused write keeps in shared memory for the norm; wider
+    #: rows are read by a kernel of their own
+    FUSED_READ_WIDTH = 10240
 
     def __init__(self, streams: int, in_name: str = "in", out_name: str = "out", mix_name: str = "mix"):
         if streams < 1:
@@ -54,7 +57,7 @@ class StreamMixing(Connection):
     def write(self, ctx, x, y, then=None):
         """Updates the streams from the sublayer's output ``y``. ``then = (connection, norm)``: the
         sublayer that follows at once; its normed input is computed in the same pass and returned."""
-        if then is None:
+        if then is None or x.shape[2] > self.FUSED_READ_WIDTH:
             self.ops.streams_update(x, self.w_mix, self.w_out, y)
             return None
         nxt, norm = then
