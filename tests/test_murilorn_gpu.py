@@ -119,7 +119,7 @@ def _paged_case(reqs, Hkv, hd, vd, ps, dt, seed=5):
     return R, T, bt, kp, vp, cu, kvl, req
 
 
-@pytest.mark.parametrize("Hq,Hkv,hd,vd", [(4, 2, 16, 32), (3, 3, 24, 8), (8, 1, 64, 64), (2, 2, 128, 96), (6, 2, 40, 40)])
+@pytest.mark.parametrize("Hq,Hkv,hd,vd", [(4, 2, 16, 32), (3, 3, 24, 8), (8, 1, 64, 64), (2, 2, 128, 96), (6, 2, 40, 40), (6, 2, 32, 48)])
 @pytest.mark.parametrize("window,keep,cap,sink", [(0, 0, 0.0, False), (40, 0, 7.0, True), (23, 5, 0.0, True), (100, 37, 9.0, False),
                                                   (1, 1, 4.0, True)])
 def test_attention_with_cap_kept_positions_and_sink(both, Hq, Hkv, hd, vd, window, keep, cap, sink):
