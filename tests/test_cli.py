@@ -82,3 +82,21 @@ def test_what_the_command_line_refuses(tmp_path, capsys):
     with pytest.raises(SystemExit):                           # the subcommand's own options are checked by the parser
         main(["generate"])
     capsys.readouterr()
+
+
+def test_init_and_inspect_with_the_third_architecture(tmp_path, capsys):
+    from tests.murilorn_cases import MA
+    cj = tmp_path / "cfg.json"
+    cj.write_text(json.dumps(MA))
+    folder = tmp_path / "model"
+    rc, out, _ = run(capsys, "init", str(folder), "--config-json", str(cj), "--seed", "3", "--store-dtype", "bfloat16")
+    assert rc == 0
+    rc, out, _ = run(capsys, "inspect", str(folder))
+    assert rc == 0 and "loadable: yes" in out and "architecture: Murilorn" in out
+    for name in ("l1.hc1.mix", "l0.mix.q.conv", "l1.mix.k.b", "l3.mlp.e3.down", "final.norm"):
+        assert name in out
+    assert "l2.norm2" not in out and "l2.hc2.in" not in out         # that layer has no feed-forward
+    # a folder of another design's tensors under this configuration: everything is named
+    (folder / "config.json").write_text(json.dumps(dict(MA, streams=2)))
+    rc, out, _ = run(capsys, "inspect", str(folder))
+    assert rc == 1 and "loadable: no" in out and "wrong shape: l0.hc1.in" in out

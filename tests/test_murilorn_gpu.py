@@ -529,3 +529,34 @@ def test_configurations_drawn_at_random(seed, tmp_path):
             check(np.concatenate(outs_a), ra, dtype, f"seed {seed}.{k}: request a", "random")
             check(np.concatenate(outs_b), rb, dtype, f"seed {seed}.{k}: request b", "random")
             assert tr.close() == 0
+
+
+def test_command_line_generates_with_sampling(tmp_path):
+    """`garuda generate` on a folder of this design: greedy tokens are the plain model's, and a
+    sampled run with a seed (temperature, top-k, top-p through the engine's sampler) repeats itself."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from tests.plain import murilorn_plain as mp
+    name = "MA"
+    d = model_dir(name)
+    cfg = tmp_path / "config.toml"
+    prompt = random_tokens(name, 11, 5)
+    exe = [sys.executable, os.path.join(helpers.ROOT, "bin", "garuda")]
+
+    def generate(sampling, *more):
+        cfg.write_text(f'[model]\npath = "{d}"\ndtype = "float32"\ncontext = 128\n[memory]\npage_size = 16\n[sampling]\n{sampling}')
+        out = subprocess.run(exe + ["--config", str(cfg), "generate", "--prompt-ids", ",".join(map(str, prompt)), *more],
+                             capture_output=True, text=True)
+        assert out.returncode == 0, out.stderr
+        return json.loads(out.stdout.strip().splitlines()[-1])
+
+    rec = generate("temperature = 0.0\nmax_tokens = 6\n")
+    seq = list(prompt)
+    for _ in range(6):
+        seq.append(int(np.argmax(mp.forward(CASES[name][0], weights(name), seq)[-1])))
+    assert rec["tokens"] == seq[len(prompt):] and rec["finish_reason"] == "length"
+    a = generate("temperature = 0.9\ntop_k = 20\ntop_p = 0.9\nmax_tokens = 8\n", "--seed", "4")
+    b = generate("temperature = 0.9\ntop_k = 20\ntop_p = 0.9\nmax_tokens = 8\n", "--seed", "4")
+    assert a["tokens"] == b["tokens"] and len(a["tokens"]) == 8
